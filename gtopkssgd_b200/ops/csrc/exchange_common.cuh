@@ -1,0 +1,152 @@
+// Device-side pieces shared by the two sparse exchange kernels (K2: gTop-k tree,
+// K2t: Top-k all-gather): the per-rank descriptor, peer pushes with flags, the
+// direct-address merge of two sparse sets, and the residual put-back.
+//
+// Merging without sorting: each rank owns an int32 table `map` of d entries.
+// To join set A (n_a entries) with set B, A first writes map[A[i].idx] = i; an
+// entry (j, v) of B is shared iff p = map[j] satisfies p < n_a && A[p].idx == j.
+// The second test makes stale table contents harmless, so the table is never
+// cleared.
+#pragma once
+#include "select_common.cuh"
+#include "host_api.h"
+
+namespace gtk {
+
+// Layout of the symmetric (peer-visible) region of one rank, identical on all
+// ranks.  Two parities (epoch & 1) so that a fast sender of call e+1 never
+// overwrites what a slow reader of call e still needs.
+//   slots : [2][kMaxRounds][kcap] pairs   receive slot of each tree round
+//   ag    : [2][kMaxPeers][kcap] pairs    all-gather slots, one per source rank (K2t only)
+//   gout  : [2][kcap] pairs               the global top-k set
+//   flags : [2][kFlagsPerParity] u64      (epoch << 32) | count
+constexpr int kFlagBcast = kMaxRounds;             // flag index of the broadcast
+constexpr int kFlagAg0 = kMaxRounds + 1;           // first all-gather flag (one per source)
+constexpr int kFlagsPerParity = kMaxRounds + 1 + kMaxPeers;
+
+struct K2Rank {
+  const Pair* sel;        // local selection written by K1
+  const K1State* st;      // st->n_sel = number of local pairs
+  Pair* work[2];          // [kcap_work] ping-pong merge buffers
+  int32_t* map;           // [d] direct-address table
+  float* resid;           // [d] residual
+  Pair* slots;            // local symmetric buffers
+  Pair* ag;
+  Pair* gout;
+  uint64_t* flags;
+  Ctrl* ctrl;
+  unsigned int* n_global; // device word: number of pairs in gout[parity]
+  Pair* peer_slots[kMaxPeers];
+  Pair* peer_ag[kMaxPeers];
+  Pair* peer_gout[kMaxPeers];
+  uint64_t* peer_flags[kMaxPeers];
+};
+
+struct ExchangeShared {
+  SelectShared sel;
+  unsigned int payload;
+  int ok;
+};
+
+__device__ __forceinline__ size_t slot_off(unsigned int parity, unsigned int round,
+                                           unsigned int kcap) {
+  return ((size_t)parity * kMaxRounds + round) * kcap;
+}
+__device__ __forceinline__ size_t ag_off(unsigned int parity, unsigned int src, unsigned int kcap) {
+  return ((size_t)parity * kMaxPeers + src) * kcap;
+}
+__device__ __forceinline__ size_t flag_off(unsigned int parity, unsigned int which) {
+  return (size_t)parity * kFlagsPerParity + which;
+}
+
+// All CTAs of the rank copy n pairs to dst (peer or local memory).
+__device__ __forceinline__ void push_pairs(Pair* dst, const Pair* src, unsigned int n,
+                                           unsigned int cta, unsigned int nct) {
+  const unsigned int stride = nct * kSelThreads;
+  for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride)
+    st_pair(&dst[i], ld_pair_cg(&src[i]));
+  __threadfence_system();
+}
+
+// One thread per CTA waits for the flag, the CTA learns the count.
+__device__ __forceinline__ bool cta_wait_flag(ExchangeShared& sh, const uint64_t* flag,
+                                              uint32_t epoch, Ctrl* ctrl, uint64_t limit_ns,
+                                              uint32_t where, unsigned int* count) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t payload = 0;
+    sh.ok = wait_flag(flag, epoch, ctrl, limit_ns, where, &payload) ? 1 : 0;
+    sh.payload = payload;
+  }
+  __syncthreads();
+  *count = sh.payload;
+  return sh.ok != 0;
+}
+
+// A <- copy of src, and map[idx] = position.
+__device__ __forceinline__ void copy_and_map(Pair* A, const Pair* src, unsigned int n, int32_t* map,
+                                             unsigned int d, unsigned int cta, unsigned int nct,
+                                             Ctrl* ctrl) {
+  const unsigned int stride = nct * kSelThreads;
+  for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride) {
+    const Pair e = ld_pair_cg(&src[i]);
+    st_pair(&A[i], e);
+    if ((unsigned int)e.idx < d) map[e.idx] = (int32_t)i;
+    else record_error(ctrl, ST_BOUNDS, 300);
+  }
+}
+
+__device__ __forceinline__ void build_map(const Pair* A, unsigned int n, int32_t* map,
+                                          unsigned int d, unsigned int cta, unsigned int nct,
+                                          Ctrl* ctrl) {
+  const unsigned int stride = nct * kSelThreads;
+  for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride) {
+    const Pair e = ld_pair_cg(&A[i]);
+    if ((unsigned int)e.idx < d) map[e.idx] = (int32_t)i;
+    else record_error(ctrl, ST_BOUNDS, 301);
+  }
+}
+
+// Shared indices: A[p].val += B[j].val and B[j] is marked dead (idx = -1).
+// B lives in local memory.  Indices are unique inside A and inside B, so every
+// A[p] is touched by at most one thread.
+__device__ __forceinline__ void probe_merge(Pair* A, unsigned int n_a, Pair* B, unsigned int n_b,
+                                            const int32_t* map, unsigned int d, unsigned int cta,
+                                            unsigned int nct, Ctrl* ctrl) {
+  const unsigned int stride = nct * kSelThreads;
+  for (unsigned int j = cta * kSelThreads + threadIdx.x; j < n_b; j += stride) {
+    const Pair e = ld_pair_cg(&B[j]);
+    if ((unsigned int)e.idx >= d) {
+      record_error(ctrl, ST_BOUNDS, 302);
+      B[j].idx = -1;
+      continue;
+    }
+    const unsigned int p = (unsigned int)__ldcg(&map[e.idx]);
+    if (p < n_a) {
+      const Pair a = ld_pair_cg(&A[p]);
+      if (a.idx == e.idx) {
+        A[p].val = a.val + e.val;
+        B[j].idx = -1;
+      }
+    }
+  }
+}
+
+// Residual put-back (compression.py:66-75 in the reference): every locally
+// selected entry whose index is not in the global set returns to the residual.
+// Requires map[] built over G.
+__device__ __forceinline__ void put_back(const Pair* sel, unsigned int n_sel, const Pair* G,
+                                         unsigned int n_g, const int32_t* map, float* resid,
+                                         unsigned int d, unsigned int cta, unsigned int nct) {
+  const unsigned int stride = nct * kSelThreads;
+  for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n_sel; i += stride) {
+    const Pair e = sel[i];
+    if ((unsigned int)e.idx >= d) continue;
+    const unsigned int p = (unsigned int)__ldcg(&map[e.idx]);
+    bool in_global = false;
+    if (p < n_g) in_global = ld_pair_cg(&G[p]).idx == e.idx;
+    if (!in_global) resid[e.idx] += e.val;
+  }
+}
+
+}  // namespace gtk

@@ -1,0 +1,235 @@
+// K2: the gTop-k recursive-doubling exchange as one persistent kernel.
+//
+// Semantics of gtopk_sparse_allreduce in the reference (allreducer.py:71-163):
+// log2(P) rounds; in round r rank i + 2^r sends its k pairs to rank i for every
+// i = 0 (mod 2^(r+1)); the receiver sums values on shared indices and keeps the k
+// largest magnitudes of the union; rank 0 ends with the global set and
+// broadcasts it; every rank returns "selected locally but not globally" values
+// to its residual (compression.py:66-75).
+//
+// Here every transfer is a plain NVLink peer store into the partner's receive
+// slot followed by a release store of an epoch-stamped flag in the partner's
+// memory; a receiver polls only its own memory.  No MPI, no NCCL, no host
+// staging, no per-round barrier between ranks.
+//
+// One launch serves gridDim.y ranks: 1 in production (one process per GPU), P
+// when all ranks are emulated on one GPU for testing, in which case the launch
+// is cooperative so that all CTAs are co-resident and the flag waits make
+// progress.  gridDim.x CTAs serve each rank and meet in RankBarrier.
+#include "exchange_common.cuh"
+
+namespace gtk {
+
+__global__ void __launch_bounds__(kSelThreads)
+k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsigned int P,
+                  unsigned int k, unsigned int kcap, unsigned int d, unsigned int epoch,
+                  unsigned long long limit_ns) {
+  __shared__ ExchangeShared sh;
+  const K2Rank& R = ranks[blockIdx.y];
+  const unsigned int me = rank_base + blockIdx.y;
+  const unsigned int cta = blockIdx.x, nct = gridDim.x;
+  const unsigned int parity = epoch & 1u;
+  Ctrl* ctrl = R.ctrl;
+  RankBarrier bar{ctrl, nct, 0u, limit_ns};
+
+  unsigned int n_sel = R.st->n_sel;
+  if (n_sel > kcap) n_sel = kcap;
+  const Pair* cur = R.sel;      // current set of this rank
+  unsigned int n_cur = n_sel;
+  bool cur_is_work = false;     // cur already lives in a writable work buffer
+  bool cur_mapped = false;      // map[] already describes cur
+  int cur_buf = 0;
+
+  unsigned int rounds = 0;
+  while ((1u << rounds) < P) ++rounds;
+
+  for (unsigned int r = 0; r < rounds; ++r) {
+    const unsigned int bit = 1u << r;
+    const unsigned int low = me & (2u * bit - 1u);
+    if (low == bit) {
+      // ---- sender: push the current set into the partner's slot, raise its flag
+      const unsigned int partner = me - bit;
+      Pair* dst = R.peer_slots[partner] + slot_off(parity, r, kcap);
+      push_pairs(dst, cur, n_cur, cta, nct);
+      if (!bar.sync(200 + r)) return;
+      if (cta == 0 && threadIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys_u64(R.peer_flags[partner] + flag_off(parity, r),
+                           ((uint64_t)epoch << 32) | (uint64_t)n_cur);
+      }
+      break;
+    }
+    if (low != 0u) break;  // already left the tree
+    // ---- receiver
+    Pair* A;
+    if (!cur_is_work) {
+      A = R.work[0];
+      copy_and_map(A, cur, n_cur, R.map, d, cta, nct, ctrl);
+      cur_buf = 0;
+    } else {
+      A = R.work[cur_buf];
+      if (!cur_mapped) build_map(A, n_cur, R.map, d, cta, nct, ctrl);
+    }
+    unsigned int n_b = 0;
+    if (!cta_wait_flag(sh, R.flags + flag_off(parity, r), epoch, ctrl, limit_ns, 210 + r, &n_b))
+      return;
+    if (n_b > kcap) {
+      record_error(ctrl, ST_CAPACITY, 220 + r);
+      n_b = kcap;
+    }
+    Pair* B = R.slots + slot_off(parity, r, kcap);
+    if (!bar.sync(230 + r)) return;  // map complete
+    probe_merge(A, n_cur, B, n_b, R.map, d, cta, nct, ctrl);
+    if (!bar.sync(240 + r)) return;  // sums complete
+    // ---- re-select the k largest magnitudes of A u live(B)
+    const unsigned int n_a = n_cur;
+    const unsigned int n_u = n_a + n_b;
+    auto key_at = [&](unsigned int i) -> uint32_t {
+      const Pair e = ld_pair_cg(i < n_a ? &A[i] : &B[i - n_a]);
+      return e.idx < 0 ? 0xffffffffu : mag_key(e.val);
+    };
+    Threshold th;
+    if (!radix_select_kth(sh.sel, bar, cta, nct, n_u, k, ctrl->hist[r], key_at, &th, 250 + 10 * r))
+      return;
+    Pair* OUT = R.work[cur_buf ^ 1];
+    int32_t* map = R.map;
+    auto on_placed = [&](Pair e, unsigned int pos) { map[e.idx] = (int32_t)pos; };
+    StagedAppender app{&sh.sel, OUT, &ctrl->cursor[r], kcap, ctrl};
+    app.begin();
+    const unsigned int stride = nct * kSelThreads;
+    const unsigned int trips = (n_u + stride - 1) / stride;
+    for (unsigned int t = 0; t < trips; ++t) {
+      const unsigned int i = t * stride + cta * kSelThreads + threadIdx.x;
+      if (i < n_u) {
+        const Pair e = ld_pair_cg(i < n_a ? &A[i] : &B[i - n_a]);
+        if (e.idx >= 0 && passes_threshold(mag_key(e.val), th, &ctrl->tie[r])) app.put(e);
+      }
+      app.end_tile(on_placed);
+    }
+    app.flush(on_placed);
+    if (!bar.sync(290 + r)) return;  // OUT and its cursor complete
+    n_cur = __ldcg(&ctrl->cursor[r]);
+    if (n_cur > kcap) n_cur = kcap;
+    cur_buf ^= 1;
+    cur = R.work[cur_buf];
+    cur_is_work = true;
+    cur_mapped = true;
+  }
+
+  // ---- broadcast of the global set (rank 0 pushes to everyone, itself included)
+  Pair* G = R.gout + (size_t)parity * kcap;
+  unsigned int n_g = 0;
+  if (me == 0u) {
+    n_g = n_cur;
+    for (unsigned int q = 0; q < P; ++q) {
+      Pair* dst = (q == 0u ? R.gout : R.peer_gout[q]) + (size_t)parity * kcap;
+      push_pairs(dst, cur, n_cur, cta, nct);
+    }
+    if (!bar.sync(400)) return;
+    if (cta == 0 && threadIdx.x == 0) {
+      __threadfence_system();
+      for (unsigned int q = 1; q < P; ++q)
+        st_release_sys_u64(R.peer_flags[q] + flag_off(parity, kFlagBcast),
+                           ((uint64_t)epoch << 32) | (uint64_t)n_cur);
+    }
+  } else {
+    if (!cta_wait_flag(sh, R.flags + flag_off(parity, kFlagBcast), epoch, ctrl, limit_ns, 410, &n_g))
+      return;
+    if (n_g > kcap) {
+      record_error(ctrl, ST_CAPACITY, 411);
+      n_g = kcap;
+    }
+  }
+  // ---- residual put-back of S_local \ S_global
+  build_map(G, n_g, R.map, d, cta, nct, ctrl);
+  if (!bar.sync(420)) return;
+  put_back(R.sel, n_sel, G, n_g, R.map, R.resid, d, cta, nct);
+  if (cta == 0 && threadIdx.x == 0) *R.n_global = n_g;
+}
+
+}  // namespace gtk
+
+using namespace gtk;
+
+extern "C" unsigned long long gtk_k2rank_bytes(void) { return sizeof(K2Rank); }
+
+// Symmetric-region geometry, in bytes, for a given kcap: offsets of slots, ag,
+// gout and flags, and the total size.  out[0..4] = {slots, ag, gout, flags, total}.
+extern "C" void gtk_symm_layout(unsigned int kcap, int with_allgather, unsigned long long* out) {
+  unsigned long long off = 0;
+  out[0] = off;
+  off += 2ull * kMaxRounds * kcap * sizeof(Pair);
+  out[1] = off;
+  if (with_allgather) off += 2ull * kMaxPeers * kcap * sizeof(Pair);
+  out[2] = off;
+  off += 2ull * kcap * sizeof(Pair);
+  off = (off + 255ull) & ~255ull;
+  out[3] = off;
+  off += 2ull * kFlagsPerParity * sizeof(uint64_t);
+  off = (off + 255ull) & ~255ull;
+  out[4] = off;
+}
+
+// Fill one K2Rank descriptor on the host (the caller copies it to the device).
+extern "C" int gtk_k2rank_fill(void* desc_host, const void* sel, const void* st, void* work0,
+                               void* work1, void* map, void* resid, void* symm_local, void* ctrl,
+                               void* n_global, unsigned int kcap, int with_allgather,
+                               unsigned int P, void* const* symm_peers) {
+  if (P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
+  unsigned long long lay[5];
+  gtk_symm_layout(kcap, with_allgather, lay);
+  K2Rank* r = (K2Rank*)desc_host;
+  r->sel = (const Pair*)sel;
+  r->st = (const K1State*)st;
+  r->work[0] = (Pair*)work0;
+  r->work[1] = (Pair*)work1;
+  r->map = (int32_t*)map;
+  r->resid = (float*)resid;
+  char* base = (char*)symm_local;
+  r->slots = (Pair*)(base + lay[0]);
+  r->ag = (Pair*)(base + lay[1]);
+  r->gout = (Pair*)(base + lay[2]);
+  r->flags = (uint64_t*)(base + lay[3]);
+  r->ctrl = (Ctrl*)ctrl;
+  r->n_global = (unsigned int*)n_global;
+  for (unsigned int q = 0; q < (unsigned int)kMaxPeers; ++q) {
+    char* pb = q < P ? (char*)symm_peers[q] : nullptr;
+    r->peer_slots[q] = pb ? (Pair*)(pb + lay[0]) : nullptr;
+    r->peer_ag[q] = pb ? (Pair*)(pb + lay[1]) : nullptr;
+    r->peer_gout[q] = pb ? (Pair*)(pb + lay[2]) : nullptr;
+    r->peer_flags[q] = pb ? (uint64_t*)(pb + lay[3]) : nullptr;
+  }
+  return GTK_OK;
+}
+
+static int k2_max_coresident(void* fn) {
+  const DeviceInfo* di = gtk_device_info();
+  if (!di) return 0;
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)fn, kSelThreads, 0) !=
+      cudaSuccess)
+    return 0;
+  return occ * di->sms;
+}
+
+// ranks_dev: device array of nranks_in_launch K2Rank descriptors (1 in production).
+// ctrl_dev[i]: control block of each of those ranks (cleared here).
+extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, unsigned int nranks,
+                               unsigned int rank_base, unsigned int P, unsigned int k,
+                               unsigned int kcap, unsigned int d, unsigned int epoch,
+                               unsigned int nctas, unsigned long long limit_ns, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (P < 2 || (P & (P - 1)) != 0 || P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
+  if (k == 0 || k > kcap || nranks == 0 || nctas == 0) return GTK_ERR_ARG;
+  const int maxco = k2_max_coresident((void*)k2_gtopk_exchange);
+  if ((int)(nranks * nctas) > maxco) return GTK_ERR_ARG;
+  for (unsigned int i = 0; i < nranks; ++i)
+    if (cudaMemsetAsync(ctrl_dev[i], 0, sizeof(Ctrl), stream) != cudaSuccess) return GTK_ERR_CUDA;
+  const K2Rank* ranks = (const K2Rank*)ranks_dev;
+  void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &epoch, &limit_ns};
+  cudaError_t e = cudaLaunchCooperativeKernel((void*)k2_gtopk_exchange, dim3(nctas, nranks),
+                                              dim3(kSelThreads), args, 0, stream);
+  gtk_count_launch(1);
+  if (e != cudaSuccess) return GTK_ERR_CUDA;
+  return GTK_OK;
+}
