@@ -1,0 +1,232 @@
+"""Headline benchmark: training throughput (samples/s) of gTop-k S-SGD at
+density 0.001 on N GPUs of one node, ResNet-50 / batch 64 per GPU / fp32 /
+synthetic ImageNet-shaped data, plus the per-iteration communication time.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+
+Prints one JSON line on rank 0.  ``value`` is the whole-job samples/s timed on
+the device (CUDA events, barrier + synchronize on both sides, max over ranks)
+with the batch already resident on the GPU; ``e2e`` is the same loop through
+the public trainer API (``DLTrainer.train`` + ``update_model``) with the batch
+copied from pinned host memory every step and the loss read back every step.
+``--impl reference`` is the reference arm: it reports why the unmodified
+reference cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# Per-worker images/s of the reference's gTop-k runs (scripts/icdcs2019/communication.py:492 for
+# ResNet-50, :477 VGG-16, :482 ResNet-20, :497 LSTM-PTB), P = 1, 4, 8 workers.
+PUBLISHED_PER_WORKER = {
+    "resnet50": {1: 52.873, 4: 39.795, 8: 39.713},
+    "vgg16": {1: 1317.333, 4: 131.060, 8: 130.551},
+    "resnet20": {1: 920.632, 4: 916.260, 8: 868.730},
+    "lstm": {1: 392.0, 4: 17.8, 8: 17.6},
+}
+MODEL_DEFAULTS = {  # dataset, per-GPU batch, lr
+    "resnet50": ("imagenet", 64, 0.1),
+    "vgg16": ("cifar10", 128, 0.1),
+    "resnet20": ("cifar10", 32, 0.1),
+    "lstm": ("ptb", 20, 22.0),
+    "alexnet": ("imagenet", 256, 0.01),
+}
+
+
+def reference_arm(args):
+    reason = ("reference is not installable (no setup.py/pyproject.toml) and imports mpi4py, horovod and "
+              "tensorboardX at module load, none of which exist in this image; it is also Python-2-only "
+              "(dl_trainer.py:490 .next(), allreducer.py:115 range.index)")
+    print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", type=str, default="resnet50", choices=sorted(MODEL_DEFAULTS))
+    ap.add_argument("--batch-size", type=int, default=None, help="per-GPU batch (default: the named config's)")
+    ap.add_argument("--density", type=float, default=0.001)
+    ap.add_argument("--compressor", type=str, default="gtopk", choices=["gtopk", "topk", "topk2", "none"])
+    ap.add_argument("--threshold", type=int, default=None, help="merge threshold in elements (default: one group)")
+    ap.add_argument("--channels-last", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.ops import lib as native
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel import distributed_optimizer as dopt
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.trainer.dl_trainer import DLTrainer
+    from gtopkssgd_b200.utils.timing import ClockSampler
+
+    settings.PIN_DENSITY = True  # the named configs fix the density at 0.001 from the first step
+    settings.logger.setLevel("WARNING")
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "bench.py needs a CUDA device"}), flush=True)
+        return 1
+    torch.backends.cudnn.benchmark = True
+    torch.backends.cudnn.allow_tf32 = False          # strict fp32, as the reference trains
+    torch.backends.cuda.matmul.allow_tf32 = False
+    local_rank = comm.env_local_rank()
+    device = torch.device("cuda", local_rank % torch.cuda.device_count())
+    torch.cuda.set_device(device)
+    comm.init()
+    rank, world = comm.rank(), comm.size()
+    if world != args.gpus:
+        if rank == 0:
+            print(json.dumps({"error": "--gpus %d but world size is %d" % (args.gpus, world)}), flush=True)
+        return 1
+
+    dataset, bs, lr = MODEL_DEFAULTS[args.model]
+    bs = args.batch_size or bs
+    sparse = args.compressor != "none"
+    trainer = DLTrainer(rank, world, dist=False, batch_size=bs, is_weak_scaling=True, ngpus=1, data_dir="synthetic",
+                        dataset=dataset, dnn=args.model, lr=lr, nworkers=world, device=device,
+                        synthetic_train_size=max(4096, bs * world * 64))
+    if args.channels_last and args.model not in ("lstm",):
+        trainer.net.to(memory_format=torch.channels_last)
+    comm.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
+    optimizer = dopt.DistributedOptimizer(trainer.optimizer, trainer.net.named_parameters(),
+                                          compression=compressors[args.compressor], is_sparse=sparse,
+                                          density=args.density, threshold=args.threshold)
+    trainer.update_optimizer(optimizer)
+    net, crit = trainer.net, trainer.criterion
+    is_lstm = args.model == "lstm"
+
+    # ---- a few batches in pinned host memory (e2e) and one resident on the device (kernel-only)
+    host_batches = []
+    it = iter(trainer.trainloader)
+    for _ in range(4):
+        x, y = next(it)
+        host_batches.append((x.pin_memory(), y.pin_memory()))
+    h2d_bytes = sum(t.numel() * t.element_size() for t in host_batches[0])
+    dev_x, dev_y, _, _ = trainer._to_device(host_batches[0])
+    if args.channels_last and dev_x.dim() == 4:
+        dev_x = dev_x.contiguous(memory_format=torch.channels_last)
+    hidden = net.init_hidden() if is_lstm else None
+
+    def device_step():
+        nonlocal hidden
+        optimizer.zero_grad()
+        if is_lstm:
+            from gtopkssgd_b200.models.lstm import repackage_hidden
+            hidden = repackage_hidden(hidden)
+            out, hidden = net(dev_x, hidden)
+            loss = crit(out.view(-1, net.vocab_size), dev_y.reshape(-1))
+        else:
+            loss = crit(net(dev_x), dev_y)
+        loss.backward()
+        if is_lstm:
+            optimizer.clip_grad_norm(0.25)
+        optimizer.step()
+        return loss
+
+    e2e_state = {"hidden": net.init_hidden() if is_lstm else None, "i": 0}
+
+    def e2e_step():
+        batch = host_batches[e2e_state["i"] % len(host_batches)]
+        e2e_state["i"] += 1
+        optimizer.zero_grad()
+        if is_lstm:
+            _, e2e_state["hidden"] = trainer.train(1, data=batch, hidden=e2e_state["hidden"])
+            optimizer.clip_grad_norm(0.25)
+        else:
+            trainer.train(1, data=batch)
+        trainer.update_model()
+        return trainer.loss  # device -> host read of this step's loss
+
+    def timed(fn, steps):
+        comm.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        wall = time.time() - t0
+        comm.barrier()
+        dev_s = a.elapsed_time(b) * 1e-3
+        return comm.allreduce_max_float(dev_s, device), comm.allreduce_max_float(wall, device)
+
+    for _ in range(args.warmup):
+        device_step()
+    torch.cuda.synchronize()
+    optimizer.check_status()
+    sampler = ClockSampler(gpu_index=device.index or 0)
+    if rank == 0:
+        sampler.start()
+    native.reset_launch_count()
+    dev_s, _ = timed(device_step, args.steps)
+    launches = native.launch_count()
+    clocks = sampler.stop() if rank == 0 else {}
+    optimizer.check_status()
+
+    e2e = None
+    if not args.skip_e2e:
+        for _ in range(max(2, args.warmup // 2)):
+            e2e_step()
+        e2e_dev_s, e2e_wall = timed(e2e_step, args.steps)
+        e2e = {"value": bs * world * args.steps / e2e_wall, "unit": "samples/s", "h2d_bytes_per_step": h2d_bytes,
+               "d2h_bytes_per_step": 4, "ms_per_step": e2e_wall / args.steps * 1e3,
+               "timing": "host wall clock around K steps, each ending in a blocking loss read; max over ranks"}
+
+    # ---- per-iteration communication time: select (K1) and exchange (K2 + put-back), device-timed
+    comm_ms = {}
+    a = optimizer._allreducer
+    for e in a.engines:
+        m = a.timers.means(e.g.key)
+        comm_ms = {"select_ms": m["compression"] * 1e3, "exchange_ms": m["allreduce"] * 1e3}
+    sel_stats = a.engines[0].selector.stats() if sparse else {}
+
+    value = bs * world * args.steps / dev_s
+    pub = PUBLISHED_PER_WORKER.get(args.model, {}).get(world)
+    out = {
+        "metric": "samples/sec at density %g (gTop-k S-SGD training throughput)" % args.density,
+        "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / (pub * world)) if pub else None, "dtype": "fp32", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": args.model, "global_batch": bs * world, "per_gpu_batch": bs,
+                   "seq_len": 35 if is_lstm else None, "parallelism": "dp%d" % world,
+                   "compressor": args.compressor, "density": args.density, "lr": lr,
+                   "optimizer": "momentum SGD (fused flat-buffer step)",
+                   "l2": "inputs larger than L2 (activations and gradients exceed 126 MB per step); no flush",
+                   "merge_groups": len(a.engines), "channels_last": bool(args.channels_last),
+                   "tf32": False},
+        "comm_ms_per_iter": comm_ms,
+        "select_stats": sel_stats,
+        "clocks": clocks,
+        "e2e": e2e,
+        "gpu_launches": int(launches),
+    }
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    optimizer.stop()
+    comm.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

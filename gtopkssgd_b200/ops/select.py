@@ -33,7 +33,7 @@ class TopkSelector:
     """
 
     def __init__(self, numel: int, max_k: int, device: torch.device, target_ratio: float = 3.0,
-                 cap_factor: int = 16, limit_ms: float = 2000.0):
+                 cap_factor: int = 32, limit_ms: float = 2000.0):
         if numel >= 2 ** 31:
             raise ValueError("a merged group must have fewer than 2^31 elements")
         self.numel = int(numel)

@@ -1,0 +1,111 @@
+"""Process-group plumbing: one process per GPU over ``torch.distributed``.
+
+NCCL (over NVLink/NVSwitch) when CUDA is present, gloo on CPU.  The reference
+takes rank and size from ``MPI.COMM_WORLD`` (distributed_optimizer.py:207-211)
+and broadcasts weights / epoch / iteration with Horovod and mpi4py
+(gtopk_trainer.py:39-40,51); the helpers here give the same services on the
+process group.  A single process without any launcher is a world of size 1.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from typing import Any, Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+_cpu_group = None
+
+
+def env_rank() -> int:
+    return int(os.environ.get("RANK", "0"))
+
+
+def env_world_size() -> int:
+    return int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def env_local_rank() -> int:
+    return int(os.environ.get("LOCAL_RANK", os.environ.get("RANK", "0")))
+
+
+def init(backend: Optional[str] = None, timeout_s: float = 1800.0, device: Optional[torch.device] = None) -> None:
+    """Join the process group described by RANK / WORLD_SIZE / MASTER_* (the
+    torchrun contract).  Does nothing for a single process or when the group
+    already exists."""
+    global _cpu_group
+    if env_world_size() <= 1 or dist.is_initialized():
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    if backend is None:
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+    kwargs: Dict[str, Any] = {}
+    if backend == "nccl":
+        dev = device or torch.device("cuda", env_local_rank() % max(torch.cuda.device_count(), 1))
+        torch.cuda.set_device(dev)
+        kwargs["device_id"] = dev
+    dist.init_process_group(backend=backend, rank=env_rank(), world_size=env_world_size(),
+                            timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    if backend == "nccl":
+        _cpu_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
+
+
+def cpu_group():
+    """A gloo group for host-side object exchange (None = the default group)."""
+    return _cpu_group
+
+
+def shutdown() -> None:
+    global _cpu_group
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    _cpu_group = None
+
+
+def rank() -> int:
+    return dist.get_rank() if dist.is_initialized() else 0
+
+
+def size() -> int:
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
+def barrier() -> None:
+    if dist.is_initialized():
+        dist.barrier(group=_cpu_group) if _cpu_group is not None else dist.barrier()
+
+
+def broadcast_object(obj: Any, root: int = 0) -> Any:
+    """mpi4py-style ``comm.bcast`` of a small Python object."""
+    if not dist.is_initialized():
+        return obj
+    box = [obj]
+    dist.broadcast_object_list(box, src=root, group=_cpu_group)
+    return box[0]
+
+
+def broadcast_parameters(state: Dict[str, torch.Tensor], root_rank: int = 0) -> None:
+    """In-place broadcast of every tensor of a ``state_dict`` (weights and BN
+    buffers) from ``root_rank``; the equivalent of hvd.broadcast_parameters."""
+    if not dist.is_initialized():
+        return
+    for _, t in sorted(state.items()):
+        if not torch.is_tensor(t):
+            continue
+        if t.is_floating_point() or t.dtype in (torch.int64, torch.int32, torch.uint8, torch.bool):
+            buf = t if t.is_contiguous() else t.contiguous()
+            dist.broadcast(buf, src=root_rank)
+            if buf is not t:
+                t.copy_(buf)
+
+
+def allreduce_max_float(value: float, device: Optional[torch.device] = None) -> float:
+    if not dist.is_initialized():
+        return value
+    dev = device or (torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl"
+                     else torch.device("cpu"))
+    t = torch.tensor([value], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())

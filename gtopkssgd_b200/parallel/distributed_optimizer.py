@@ -1,0 +1,282 @@
+"""DistributedOptimizer: wraps a torch optimizer, reduces gradients group by
+group while backward is still running, and applies the update with the fused
+K3 kernels.
+
+Public surface of the reference (distributed_optimizer.py:21-212):
+``DistributedOptimizer(optimizer, named_parameters, compression, is_sparse,
+err_handler, layerwise_times, sigma_scale, density, norm_clip, writer)``
+returns an instance of a dynamic subclass of the wrapped optimizer's class
+with ``step() synchronize() stop() add_train_epoch() get_current_density()``,
+the ``local`` switch for gradient accumulation and ``momentum_correction``;
+module-level ``rank()`` and ``size()``.
+
+Differences in mechanism, not in semantics:
+* per-parameter hooks only count arrivals; when the last gradient of a merged
+  group has been produced an event is recorded and the group's select +
+  exchange kernels are enqueued on a side stream (no device synchronisation,
+  no host thread, no queue);
+* ``synchronize()`` makes the compute stream wait for that side stream;
+* ``step()`` is two launches over the flat buffers (dense part + k sparse
+  pairs) instead of three launches per tensor; weight decay is applied after
+  sparsification and the first momentum step is ``buf = d_p`` as in the
+  reference (distributed_optimizer.py:126-137).
+"""
+from __future__ import annotations
+
+import threading
+from typing import Optional
+
+import torch
+
+from .. import settings
+from ..ops.clip import ClipNorm
+from ..ops.sgd import SgdHyper, scatter_dense, sgd_dense, sgd_sparse
+from ..settings import logger
+from . import allreducer as ar
+from . import comm
+from .compression import NoneCompressor
+from .flat_buffer import FlatBuffers
+
+
+class _DistributedOptimizer(torch.optim.Optimizer):
+    def __init__(self, params, named_parameters, compressor, is_sparse=True, err_handler=None, layerwise_times=None,
+                 sigma_scale=2.5, density=0.01, norm_clip=None, writer=None, threshold=None, overlap=True,
+                 wait_limit_ms=None):
+        super(self.__class__, self).__init__(params)
+        self._compressor = compressor
+        self._sparse = is_sparse
+        self._layerwise_times = layerwise_times
+        named_parameters = list(named_parameters) if named_parameters is not None else []
+        if any(not isinstance(p, tuple) for p in named_parameters):
+            raise ValueError("named_parameters should be a sequence of tuples (name, parameter), "
+                             "usually produced by model.named_parameters().")
+        if not named_parameters:
+            named_parameters = [("allreduce.noname.%s" % i, v) for pg in self.param_groups
+                                for i, v in enumerate(pg["params"])]
+        owned = {id(p) for pg in self.param_groups for p in pg["params"]}
+        named_parameters = [(n, p) for n, p in named_parameters if id(p) in owned and p.requires_grad]
+        self._parameter_names = {p: n for n, p in named_parameters}
+        self._lock, self._key_lock = threading.Lock(), threading.Lock()
+        self.momentum_correction = False
+        self.local = False
+        self._synced = False
+        self._step_count = 0
+        self._materialized = False
+        thr = settings.THRESHOLD if threshold is None else threshold
+        self._flat = FlatBuffers(named_parameters, thr, with_residual=True)
+        self._allreducer = ar.AllReducer(named_parameters, self._lock, self._key_lock, compressor, sparse=is_sparse,
+                                         err_callback=err_handler, layerwise_times=layerwise_times,
+                                         sigma_scale=sigma_scale, density=density, norm_clip=norm_clip, writer=writer,
+                                         flat=self._flat, wait_limit_ms=wait_limit_ms)
+        dev = self._flat.device
+        self._is_cuda = dev.type == "cuda"
+        self._overlap = overlap and self._is_cuda
+        self._comm_stream = torch.cuda.Stream(device=dev) if self._is_cuda else None
+        self._arrived = [0] * len(self._flat.groups)
+        self._launched = [False] * len(self._flat.groups)
+        self._expected = [len(g.names) for g in self._flat.groups]
+        self._post_clip: Optional[ClipNorm] = None
+        self._post_coef: Optional[torch.Tensor] = None
+        self._hook_handles = []
+        self._register_hooks()
+        uniform = all(all(pg.get(k, 0) == self.param_groups[0].get(k, 0)
+                          for k in ("lr", "momentum", "dampening", "weight_decay", "nesterov"))
+                      for pg in self.param_groups)
+        if not uniform:
+            raise ValueError("the fused step needs the same hyper-parameters in every param group")
+
+    # -- hooks -----------------------------------------------------------------
+    def _register_hooks(self):
+        for name, slot in self._flat.slots.items():
+            self._hook_handles.append(slot.param.register_post_accumulate_grad_hook(self._make_hook(slot)))
+
+    def _make_hook(self, slot):
+        gi = slot.group
+
+        def hook(p):
+            if self.local:
+                return
+            if p.grad is None or p.grad.data_ptr() != self._flat.grad.data_ptr() + 4 * slot.offset:
+                self._flat.ensure_views()
+            if self.momentum_correction:
+                self._apply_momentum_correction(slot)
+            self._arrived[gi] += 1
+            if self._arrived[gi] == self._expected[gi] and not self._launched[gi]:
+                self._launch_group(gi)
+        return hook
+
+    def _apply_momentum_correction(self, slot):
+        """Optional (off by default, distributed_optimizer.py:81-88): the
+        velocity, not the raw gradient, is what gets sparsified."""
+        buf = self._flat.momentum_view(slot.name)
+        g = self._flat.grad_view(slot.name)
+        buf.mul_(0.9).add_(g)
+        g.copy_(buf)
+
+    def _launch_group(self, gi: int) -> None:
+        self._launched[gi] = True
+        if self._comm_stream is not None and self._overlap:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._comm_stream.wait_event(ev)
+            with torch.cuda.stream(self._comm_stream):
+                self._allreducer.reduce_group(gi)
+        else:
+            self._allreducer.reduce_group(gi)
+
+    # -- public API ---------------------------------------------------------------
+    def zero_grad(self, set_to_none: bool = False):
+        """Clears the flat gradient buffer with one fill; ``p.grad`` stay views."""
+        self._flat.zero_grad()
+        self._materialized = False
+
+    def synchronize(self, materialize: bool = False):
+        """Wait (on the stream, not on the host) until every group of this
+        iteration has been reduced.  With ``materialize=True`` the dense
+        averaged gradient is also written into ``p.grad`` for callers that
+        want to look at it (the fused step does not need it)."""
+        if not self._synced:
+            for gi in range(len(self._launched)):
+                if not self._launched[gi]:  # parameters that got no gradient this iteration
+                    self._launch_group(gi)
+            if self._comm_stream is not None and self._overlap:
+                torch.cuda.current_stream().wait_stream(self._comm_stream)
+            self._synced = True
+        if materialize and not self._materialized and self._allreducer.mode != "none":
+            for eng in self._allreducer.engines:
+                r = eng.result
+                scatter_dense(eng.grad, r.pairs, r.counts, r.nseg, r.seg_stride, r.scale, r.use_atomics)
+            self._materialized = True
+
+    def clip_grad_norm(self, max_norm: float) -> torch.Tensor:
+        """Device-side ``clip_grad_norm_`` on the reduced gradient
+        (gtopk_trainer.py:81-86): the coefficient is computed from the global
+        pairs and applied inside the fused step.  Returns the device scalar."""
+        self.synchronize()
+        dev = self._flat.device
+        if self._post_clip is None:
+            self._post_clip = ClipNorm(dev)
+        a = self._allreducer
+        if a.mode == "none":
+            for eng in a.engines:
+                self._post_clip.add_dense(eng.grad)
+            self._post_coef = self._post_clip.finalize(max_norm, scale=1.0 / a.size())
+        elif any(e.result.use_atomics for e in a.engines):
+            self.synchronize(materialize=True)
+            for eng in a.engines:
+                self._post_clip.add_dense(eng.grad)
+            self._post_coef = self._post_clip.finalize(max_norm, scale=1.0)
+        else:
+            scale = 1.0
+            for eng in a.engines:
+                r = eng.result
+                self._post_clip.add_pairs(r.pairs, r.counts, r.nseg, r.seg_stride)
+                scale = r.scale
+            self._post_coef = self._post_clip.finalize(max_norm, scale=scale)
+        return self._post_coef
+
+    def _hyper(self) -> SgdHyper:
+        g = self.param_groups[0]
+        return SgdHyper(lr=float(g["lr"]), momentum=float(g.get("momentum", 0.0)),
+                        dampening=float(g.get("dampening", 0.0)), weight_decay=float(g.get("weight_decay", 0.0)),
+                        nesterov=bool(g.get("nesterov", False)))
+
+    def _step(self, closure=None):
+        """Fused update over the flat buffers.  In the sparse modes the dense
+        part (weight decay + momentum decay) does not depend on the exchange, so
+        it is enqueued before the compute stream waits for the side stream: it
+        runs while the exchange kernel is still waiting on its peers."""
+        loss = closure() if closure is not None else None
+        h = self._hyper()
+        first = self._step_count == 0
+        fb, a = self._flat, self._allreducer
+        use_buf = h.momentum != 0 and not self.momentum_correction
+        if self.momentum_correction:
+            h = SgdHyper(h.lr, 0.0, 0.0, h.weight_decay, False)
+
+        def bufs(eng):
+            return (fb.group_slice(fb.param, eng.g), fb.group_slice(fb.momentum, eng.g) if use_buf else None)
+
+        if self.local:
+            # accumulation micro-step: plain local SGD on the raw gradient
+            for eng in a.engines:
+                p, buf = bufs(eng)
+                sgd_dense(p, buf, h, first, g=eng.grad, scale=1.0)
+        elif a.mode == "none" or self._materialized:
+            self.synchronize()
+            scale = 1.0 / a.size() if a.mode == "none" else 1.0
+            for eng in a.engines:
+                p, buf = bufs(eng)
+                sgd_dense(p, buf, h, first, g=eng.grad, scale=scale, coef=self._post_coef)
+        else:
+            for eng in a.engines:
+                p, buf = bufs(eng)
+                sgd_dense(p, buf, h, first)
+            self.synchronize()
+            for eng in a.engines:
+                p, buf = bufs(eng)
+                r = eng.result
+                sgd_sparse(p, buf, r.pairs, r.counts, r.nseg, r.seg_stride, h, first, r.scale, coef=self._post_coef,
+                           use_atomics=r.use_atomics)
+        if use_buf and first:
+            for name, slot in fb.slots.items():
+                self.state[slot.param]["momentum_buffer"] = fb.momentum_view(name)
+        self._step_count += 1
+        self._post_coef = None
+        return loss
+
+    def step(self, closure=None):
+        ret = self._step(closure)
+        self._synced = False
+        self._arrived = [0] * len(self._arrived)
+        self._launched = [False] * len(self._launched)
+        a = self._allreducer
+        a.train_iter += 1
+        a.maybe_print_profiling()
+        return ret
+
+    def check_status(self):
+        """Raise GTopkTimeout if a device-side wait of the last exchange ran
+        out (synchronises).  Cheap enough for every N-th iteration."""
+        self._allreducer.check_status()
+
+    def stop(self):
+        self._allreducer.stop()
+        for h in self._hook_handles:
+            h.remove()
+        self._hook_handles = []
+
+    def add_train_epoch(self):
+        self._allreducer.train_epoch += 1
+
+    def get_current_density(self):
+        return self._allreducer.get_current_density()
+
+    # -- checkpoint helpers ------------------------------------------------------
+    def residual_state(self):
+        """Residuals by parameter name (the reference never saves them)."""
+        return {n: self._flat.residual_view(n).clone() for n in self._flat.slots}
+
+    def load_residual_state(self, state):
+        for n, t in state.items():
+            if n in self._flat.slots:
+                self._flat.residual_view(n).copy_(t)
+
+
+def DistributedOptimizer(optimizer, named_parameters=None, compression=NoneCompressor, is_sparse=False,
+                         err_handler=None, layerwise_times=None, sigma_scale=2.5, density=0.1, norm_clip=None,
+                         writer=None, threshold=None, overlap=True, wait_limit_ms=None):
+    """Wrap ``optimizer``.  The returned object is an instance of a subclass of
+    ``type(optimizer)`` that carries the methods above."""
+    cls = type(optimizer.__class__.__name__, (optimizer.__class__,), dict(_DistributedOptimizer.__dict__))
+    return cls(optimizer.param_groups, named_parameters, compression, is_sparse, err_handler, layerwise_times,
+               sigma_scale=sigma_scale, density=density, norm_clip=norm_clip, writer=writer, threshold=threshold,
+               overlap=overlap, wait_limit_ms=wait_limit_ms)
+
+
+def rank():
+    return comm.rank()
+
+
+def size(*_ignored):
+    return comm.size()

@@ -1,0 +1,193 @@
+"""gTop-k S-SGD training driver and command line
+(reference: gtopk_trainer.py:26-168, launched there with ``mpirun``; here one
+process per GPU under ``torchrun``).
+
+    torchrun --nproc-per-node 8 gtopk_trainer.py --dnn resnet20 --dataset cifar10 \
+        --data-dir synthetic --batch-size 32 --lr 0.1 --nworkers 8 \
+        --compression --compressor gtopk --density 0.001
+
+Same flags, same log-directory naming and the same throughput log line as the
+reference.  Extra flags: ``--max-iters`` (stop early), ``--threshold`` (merge
+threshold in elements), ``--pin-density`` (skip the 0.004 warm-up density of
+epoch 0), ``--save-checkpoints``.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+from .. import settings
+from ..parallel import comm
+from ..parallel import distributed_optimizer as dopt
+from ..parallel.allreducer import GTopkTimeout
+from ..parallel.compression import compressors
+from ..settings import logger
+from ..utils import create_path
+from .dl_trainer import DLTrainer, _support_datasets, _support_dnns
+
+writer = None
+relative_path = None
+
+
+def _dump_profiling_norms(optimizer, rank, epoch):
+    """PROFILING_NORM files of the reference (gtopk_trainer.py:94-126)."""
+    norms = optimizer._allreducer._profiling_norms
+    cols = list(zip(*norms)) if norms else [[], [], [], [], []]
+    names = ["gtopknorm", "randknorm", "upbound", "xnorm", "densestd"]
+    labels = ["gtopk norm", "randk norm", "upbound norm", "x norm", "dense std"]
+    for name, label, col in zip(names, labels, cols):
+        arr = np.array(col)
+        if arr.size:
+            logger.info("[rank:%d][%d] %s mean: %f, std: %f", rank, epoch, label, np.mean(arr), np.std(arr))
+        if name != "xnorm" and relative_path:
+            np.save(os.path.join(relative_path, "%s-rank%d-epoch%d.npy" % (name, rank, epoch)), arr)
+    optimizer._allreducer._profiling_norms = []
+
+
+def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, compression=False,
+                compressor="topk", nwpernode=1, sigma_scale=2.5, pretrain=None, density=0.01, prefix=None,
+                max_iters=None, threshold=None, save_checkpoints=None, check_every=50):
+    use_cuda = torch.cuda.is_available()
+    rank = dopt.rank()
+    if use_cuda:
+        torch.cuda.set_device(comm.env_local_rank() % max(torch.cuda.device_count(), 1))
+    if rank != 0:
+        pretrain = None
+    prefix = (prefix or settings.PREFIX) + "-ds%s" % str(density)
+    trainer = DLTrainer(rank, nworkers, dist=False, batch_size=batch_size, is_weak_scaling=True,
+                        ngpus=1 if use_cuda else 0, data_dir=data_dir, dataset=dataset, dnn=dnn, lr=lr,
+                        nworkers=nworkers, prefix=prefix, pretrain=pretrain, tb_writer=writer,
+                        save_checkpoints=save_checkpoints)
+    trainer.set_train_epoch(comm.broadcast_object(trainer.get_train_epoch()))
+    trainer.set_train_iter(comm.broadcast_object(trainer.get_train_iter()))
+
+    def _error_handler(new_num_workers, new_rank):
+        logger.info("Error info catched by trainer")
+        trainer.update_nworker(new_num_workers, new_rank)
+
+    comp = compressors[compressor if compression else "none"]
+    logger.info("Broadcast parameters....")
+    comm.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
+    logger.info("Broadcast parameters finished....")
+    optimizer = dopt.DistributedOptimizer(trainer.optimizer, trainer.net.named_parameters(), compression=comp,
+                                          is_sparse=compression, err_handler=_error_handler, layerwise_times=None,
+                                          sigma_scale=sigma_scale, density=density, norm_clip=None, writer=writer,
+                                          threshold=threshold)
+    trainer.update_optimizer(optimizer)
+    iters_per_epoch = trainer.get_num_of_training_samples() // (nworkers * batch_size * nsteps_update)
+    times, done = [], 0
+    display = 100 if iters_per_epoch > 100 else max(iters_per_epoch - 1, 1)
+    logger.info("Start training ....")
+    try:
+        for epoch in range(max_epochs):
+            hidden = trainer.net.init_hidden() if dnn == "lstm" else None
+            for i in range(iters_per_epoch):
+                s = time.time()
+                optimizer.zero_grad()
+                for j in range(nsteps_update):
+                    optimizer.local = j < nsteps_update - 1 and nsteps_update > 1
+                    if dnn == "lstm":
+                        _, hidden = trainer.train(1, hidden=hidden)
+                    else:
+                        trainer.train(1)
+                if dnn == "lstm":
+                    optimizer.clip_grad_norm(0.25)
+                elif dnn == "lstman4":
+                    optimizer.clip_grad_norm(400)
+                trainer.update_model()
+                if i % display == 0 or (check_every and done % check_every == 0):
+                    if use_cuda:
+                        torch.cuda.synchronize()
+                    optimizer.check_status()
+                times.append(time.time() - s)
+                if i % display == 0 and i > 0:
+                    t = float(np.mean(times))
+                    logger.info("Time per iteration including communication: %f. Speed: %f images/s, "
+                                "current density: %f", t, batch_size * nsteps_update / t,
+                                optimizer.get_current_density())
+                    times = []
+                done += 1
+                if max_iters and done >= max_iters:
+                    return trainer
+            optimizer.add_train_epoch()
+            if settings.PROFILING_NORM:
+                _dump_profiling_norms(optimizer, rank, epoch)
+    except GTopkTimeout as exc:
+        logger.error("training stopped: %s", exc)
+        raise
+    finally:
+        optimizer.stop()
+    return trainer
+
+
+def build_parser():
+    p = argparse.ArgumentParser(description="AllReduce trainer")
+    p.add_argument("--batch-size", type=int, default=32)
+    p.add_argument("--nsteps-update", type=int, default=1)
+    p.add_argument("--nworkers", type=int, default=1, help="Just for experiments, and it cannot be used in production")
+    p.add_argument("--nwpernode", type=int, default=1, help="Number of workers per node")
+    p.add_argument("--compression", dest="compression", action="store_true")
+    p.add_argument("--compressor", type=str, default="topk", choices=list(compressors.keys()),
+                   help="Specify the compressors if 'compression' is open")
+    p.add_argument("--sigma-scale", type=float, default=2.5, help="Maximum sigma scaler for sparsification")
+    p.add_argument("--density", type=float, default=0.01, help="Density for sparsification")
+    p.add_argument("--dataset", type=str, default="imagenet", choices=_support_datasets)
+    p.add_argument("--dnn", type=str, default="resnet50", choices=_support_dnns)
+    p.add_argument("--data-dir", type=str, default="./data", help="Specify the data root path, or 'synthetic'")
+    p.add_argument("--lr", type=float, default=0.1, help="Default learning rate")
+    p.add_argument("--max-epochs", type=int, default=90, help="Default maximum epochs to train")
+    p.add_argument("--pretrain", type=str, default=None, help="Specify the pretrain path")
+    p.add_argument("--max-iters", type=int, default=None, help="Stop after this many iterations")
+    p.add_argument("--threshold", type=int, default=None, help="Merge threshold in elements")
+    p.add_argument("--pin-density", action="store_true", help="Use --density from epoch 0 on")
+    p.add_argument("--save-checkpoints", action="store_true", help="Write a checkpoint at every epoch end")
+    p.set_defaults(compression=False)
+    return p
+
+
+def main(argv=None):
+    global writer, relative_path
+    args = build_parser().parse_args(argv)
+    if args.pin_density:
+        settings.PIN_DENSITY = True
+    comm.init()
+    if comm.size() > 1 and args.nworkers != comm.size():
+        logger.warning("--nworkers %d differs from the launched world size %d; using %d", args.nworkers, comm.size(),
+                       comm.size())
+        args.nworkers = comm.size()
+    batch_size = args.batch_size * args.nsteps_update
+    prefix = settings.PREFIX
+    if args.compression:
+        prefix = "comp-" + args.compressor + "-" + prefix
+    logdir = "allreduce-%s/%s-n%d-bs%d-lr%.4f-ns%d-sg%.2f-ds%s" % (prefix, args.dnn, args.nworkers, batch_size,
+                                                                     args.lr, args.nsteps_update, args.sigma_scale,
+                                                                     str(args.density))
+    relative_path = create_path("./logs/%s" % logdir)
+    rank = dopt.rank()
+    if rank == 0 and settings.TENSORBOARD:
+        try:
+            from torch.utils.tensorboard import SummaryWriter
+            writer = SummaryWriter("./runs/%s" % logdir)
+        except Exception:  # tensorboard is optional
+            writer = None
+    settings.add_file_handler(os.path.join(relative_path, settings.hostname + "-" + str(rank) + ".log"))
+    logger.info("Configurations: %s", args)
+    logger.info("Interpreter: %s", sys.version)
+    try:
+        robust_ssgd(args.dnn, args.dataset, args.data_dir, args.nworkers, args.lr, args.batch_size,
+                    args.nsteps_update, args.max_epochs, args.compression, args.compressor, args.nwpernode,
+                    args.sigma_scale, args.pretrain, args.density, prefix, max_iters=args.max_iters,
+                    threshold=args.threshold, save_checkpoints=args.save_checkpoints or None)
+    finally:
+        if writer is not None:
+            writer.close()
+        comm.shutdown()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,100 @@
+"""Rank functions used by the multi-process tests (imported by name in the
+spawned children)."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+def _make_batch(rank, it, bs):
+    g = torch.Generator().manual_seed(1000 * it + rank)
+    return torch.randn(bs, 3, 32, 32, generator=g), torch.randint(0, 10, (bs,), generator=g)
+
+
+def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="cpu"):
+    """BASELINE config: ResNet-20, batch 32 per worker would be slow on CPU;
+    batch 8 keeps the same code path.  Returns the final flat parameters."""
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.models import create_net
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("WARNING")
+    torch.set_num_threads(1)
+    dev = torch.device("cpu")
+    if device_kind == "cuda":
+        dev = torch.device("cuda", rank)
+        torch.cuda.set_device(dev)
+    comm.init(backend="gloo" if device_kind == "cpu" else "nccl")
+    torch.manual_seed(0)
+    net, _ = create_net(10, "resnet20")
+    net.to(dev)
+    comm.broadcast_parameters(net.state_dict(), 0)
+    opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+    sparse = compressor != "none"
+    dopt = DistributedOptimizer(opt, net.named_parameters(), compression=compressors[compressor], is_sparse=sparse,
+                                density=density, wait_limit_ms=20000)
+    crit = torch.nn.CrossEntropyLoss()
+    fb = dopt._flat
+    trace = {"p0": fb.param.detach().cpu().clone(), "grads": [], "params": [], "resid": []}
+    for it in range(iters):
+        x, y = _make_batch(rank, it, 8)
+        dopt.zero_grad()
+        crit(net(x.to(dev)), y.to(dev)).backward()
+        trace["grads"].append(fb.grad.detach().cpu().clone())  # raw local gradient (selection does not modify it)
+        dopt.step()
+        trace["params"].append(fb.param.detach().cpu().clone())
+        trace["resid"].append(fb.residual.detach().cpu().clone())
+    if device_kind == "cuda":
+        torch.cuda.synchronize()
+        dopt.check_status()
+    trace["numel"] = fb.numel
+    dopt.stop()
+    comm.shutdown()
+    return trace
+
+
+def failing_peer_worker(rank, world, mode):
+    """Fault injection on the host: rank 1 leaves (or stalls) before the
+    exchange; rank 0 must get a PeerTimeout / err_handler call, not a hang."""
+    import time
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.models import create_net
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.allreducer import GTopkTimeout
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("CRITICAL")
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=30)
+    torch.manual_seed(0)
+    net, _ = create_net(10, "resnet20")
+    calls = []
+    opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
+    dopt = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                                density=0.001, err_handler=lambda n, r: calls.append((n, r)), wait_limit_ms=1500)
+    crit = torch.nn.CrossEntropyLoss()
+    x, y = _make_batch(rank, 0, 4)
+    dopt.zero_grad()
+    crit(net(x), y).backward()
+    dopt.step()  # one good iteration with both ranks
+    if rank == 1:
+        if mode == "exit":
+            os._exit(0)  # leaves between steps, nothing in flight
+        if mode == "stall":
+            time.sleep(6.0)
+            return "stalled"
+    dopt.zero_grad()
+    t0 = time.time()
+    try:
+        crit(net(x), y).backward()  # on CPU the group is reduced inside the last gradient hook
+        dopt.step()
+        return "no error"
+    except GTopkTimeout:
+        return ("timeout", round(time.time() - t0, 1), calls)

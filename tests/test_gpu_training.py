@@ -1,0 +1,41 @@
+"""GPU end-to-end tests: the DistributedOptimizer on CUDA (fused select,
+fused sparse SGD step, side stream) replayed against the oracle, on one GPU
+and -- when the box has them -- on 2 and 4 GPUs through the peer-store
+exchange kernel over CUDA IPC."""
+import pytest
+import torch
+
+import _workers
+from test_distributed_cpu import replay_and_check
+from gtopkssgd_b200.utils.launch import spawn_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("compressor", ["gtopk", "none"])
+def test_single_gpu_training_matches_oracle(compressor):
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 1, args=(4, 0.001, compressor, "cuda"), timeout_s=600)
+    replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("compressor", ["gtopk", "topk", "topk2", "none"])
+def test_two_gpu_training_matches_oracle(compressor):
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 2, args=(4, 0.001, compressor, "cuda"), timeout_s=600,
+                         env=env)
+    replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.multigpu
+def test_four_gpu_gtopk_matches_oracle():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 4, args=(3, 0.001, "gtopk", "cuda"), timeout_s=600,
+                         env={"NCCL_NVLS_ENABLE": "0"})
+    replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
+
+
+def test_graft_smoke():
+    import __graft_entry__ as g
+    g.smoke()
