@@ -46,6 +46,8 @@ def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="
         x, y = _make_batch(rank, it, 8)
         dopt.zero_grad()
         crit(net(x.to(dev)), y.to(dev)).backward()
+        if compressor == "none":
+            dopt.synchronize()  # the in-place all-reduce must be complete before the buffer is recorded
         trace["grads"].append(fb.grad.detach().cpu().clone())  # raw local gradient (selection does not modify it)
         dopt.step()
         trace["params"].append(fb.param.detach().cpu().clone())

@@ -76,7 +76,7 @@ def test_k1_unaligned_views_and_scale():
     scale = torch.tensor([0.5], device=DEV)
     for off in (1, 2, 3):
         g, r = big_g[off:off + d], big_r[off:off + d]
-        r.zero_()
+        big_r.zero_()
         sel = _selector(d, k)
         for _ in range(2):
             r_before = r.clone()
