@@ -305,3 +305,114 @@ extern "C" int gtk_k1_select(const float* g, float* r, const float* g_scale, lon
   if (e != cudaSuccess) return GTK_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in k1_select_noalloc.h).
+// The scratch that gtk_k1_select takes from its caller lives here in a static
+// device array; the kernels are the ones above, unchanged.
+// ---------------------------------------------------------------------------
+#include <mutex>
+#include "k1_select_noalloc.h"
+
+namespace {
+
+constexpr unsigned int kNoAllocMaxK = 16384u;
+constexpr unsigned int kNoAllocCap = 131072u;                         // candidate pairs (8 x max k)
+constexpr size_t kNoAllocCtrlOff = 0;
+constexpr size_t kNoAllocStateOff = (sizeof(Ctrl) + 255) / 256 * 256;
+constexpr size_t kNoAllocCandOff = kNoAllocStateOff + 256;
+constexpr size_t kNoAllocBytes = kNoAllocCandOff + (size_t)kNoAllocCap * sizeof(Pair);
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never an address.
+static __device__ __align__(256) unsigned char g_k1_noalloc_scratch[kNoAllocBytes];
+
+__global__ void k1_noalloc_reset_state(K1State* st) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    st->tau = __int_as_float(0x7f800000);  // +inf: the next call takes the exact path
+    st->n_sel = 0u;
+    st->n_cand = 0u;
+    st->fallback = 0u;
+    st->n_fallbacks = 0u;
+    st->n_calls = 0u;
+    st->kth_mag = 0.f;
+    st->reserved = 0u;
+  }
+}
+
+__global__ void k1_noalloc_publish_count(const K1State* st, unsigned int* n_sel_out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *n_sel_out = st->n_sel;
+}
+
+struct NoAllocDevice {
+  unsigned char* base = nullptr;  // device address of g_k1_noalloc_scratch on this device
+  int finish_grid = 0;
+};
+std::mutex g_noalloc_mu;
+NoAllocDevice g_noalloc_dev[64];
+
+}  // namespace
+
+extern "C" unsigned int gtk_k1_noalloc_max_k(void) { return kNoAllocMaxK; }
+extern "C" unsigned long long gtk_k1_noalloc_scratch_bytes(void) { return kNoAllocBytes; }
+
+extern "C" int gtk_k1_select_noalloc(const float* g, float* r, long long d, unsigned int k,
+                                     void* sel_out, unsigned int* n_sel_out, int reset_threshold,
+                                     void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (k > kNoAllocMaxK) return GTK_ERR_TOO_LARGE;
+  if (d <= 0 || d >= (1ll << 31) || k == 0 || !g || !r || !sel_out) return GTK_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(g) & 15u) != (reinterpret_cast<uintptr_t>(r) & 15u) ||
+      (reinterpret_cast<uintptr_t>(r) & 3u) != 0u)
+    return GTK_ERR_ARG;
+  const DeviceInfo* di = gtk_device_info();
+  if (!di || di->device < 0 || di->device >= 64) return GTK_ERR_CUDA;
+  NoAllocDevice dev;
+  bool first = false;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocDevice& slot = g_noalloc_dev[di->device];
+    if (!slot.base) {
+      // once per device, with that device current
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_k1_noalloc_scratch) != cudaSuccess || !p) return GTK_ERR_CUDA;
+      int occ = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k1_finish, kSelThreads, 0) !=
+              cudaSuccess || occ < 1)
+        return GTK_ERR_CUDA;
+      slot.finish_grid = di->sms * (occ > 2 ? 2 : occ);
+      slot.base = static_cast<unsigned char*>(p);
+      first = true;
+    }
+    dev = slot;
+  }
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(dev.base + kNoAllocCtrlOff);
+  K1State* st = reinterpret_cast<K1State*>(dev.base + kNoAllocStateOff);
+  Pair* cand = reinterpret_cast<Pair*>(dev.base + kNoAllocCandOff);
+  unsigned int cap = kNoAllocCap;
+  if (first || reset_threshold) {
+    k1_noalloc_reset_state<<<1, 32, 0, stream>>>(st);
+    gtk_count_launch(1);
+  }
+  // the control block must start at zero; everything else in the scratch is overwritten before use
+  if (cudaMemsetAsync(ctrl, 0, sizeof(Ctrl), stream) != cudaSuccess) return GTK_ERR_CUDA;
+  const long long nvec = d / 4;
+  const long long tile = (long long)kK1Threads * kK1Vec;
+  const long long ntiles = (nvec + tile - 1) / tile;
+  int grid = di->sms * 2;
+  if (ntiles < grid) grid = ntiles > 0 ? (int)ntiles : 1;
+  k1_stream<<<grid, kK1Threads, 0, stream>>>(g, r, nullptr, st, cand, cap, ctrl, d);
+  gtk_count_launch(1);
+  Pair* sel = static_cast<Pair*>(sel_out);
+  float target_ratio = 3.0f;
+  unsigned long long limit_ns = 2000000000ull;
+  void* args[] = {&r, &d, &cand, &cap, &sel, &k, &st, &ctrl, &target_ratio, &limit_ns};
+  if (cudaLaunchCooperativeKernel((void*)k1_finish, dim3(dev.finish_grid), dim3(kSelThreads), args,
+                                  0, stream) != cudaSuccess)
+    return GTK_ERR_CUDA;
+  gtk_count_launch(1);
+  if (n_sel_out) {
+    k1_noalloc_publish_count<<<1, 32, 0, stream>>>(st, n_sel_out);
+    gtk_count_launch(1);
+  }
+  return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
+}
