@@ -36,6 +36,15 @@ def test_four_gpu_gtopk_matches_oracle():
     replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
 
 
+@pytest.mark.multigpu
+def test_eight_gpu_gtopk_matches_oracle():
+    if torch.cuda.device_count() < 8:
+        pytest.skip("needs 8 GPUs")
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 8, args=(3, 0.001, "gtopk", "cuda"), timeout_s=600,
+                         env={"NCCL_NVLS_ENABLE": "0"})
+    replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
+
+
 def test_graft_smoke():
     import __graft_entry__ as g
     g.smoke()
