@@ -102,7 +102,7 @@ class DeepSpeech(nn.Module):
         self._version = "0.0.1"
         self._hidden_size, self._hidden_layers, self._rnn_type = rnn_hidden_size, nb_layers, rnn_type
         self._audio_conf = audio_conf or {}
-        self._labels, self._bidirectional = labels, bidirectional
+        self._labels, self._bidirectional, self._context = labels, bidirectional, context
         sample_rate = self._audio_conf.get("sample_rate", 16000)
         window_size = self._audio_conf.get("window_size", 0.02)
         self.conv = MaskConv(nn.Sequential(
@@ -156,7 +156,7 @@ class DeepSpeech(nn.Module):
         pkg = {"version": m._version, "hidden_size": m._hidden_size, "hidden_layers": m._hidden_layers,
                "rnn_type": supported_rnns_inv.get(m._rnn_type, m._rnn_type.__name__.lower()),
                "audio_conf": m._audio_conf, "labels": m._labels, "state_dict": m.state_dict(),
-               "bidirectional": m._bidirectional}
+               "bidirectional": m._bidirectional, "context": m._context}
         if optimizer is not None:
             pkg["optim_dict"] = optimizer.state_dict()
         for key, val in (("avg_loss", avg_loss), ("iteration", iteration), ("meta", meta)):
@@ -172,7 +172,8 @@ class DeepSpeech(nn.Module):
     def load_model_package(cls, package):
         model = cls(rnn_hidden_size=package["hidden_size"], nb_layers=package["hidden_layers"],
                     labels=package["labels"], audio_conf=package["audio_conf"],
-                    rnn_type=supported_rnns[package["rnn_type"]], bidirectional=package.get("bidirectional", True))
+                    rnn_type=supported_rnns[package["rnn_type"]], bidirectional=package.get("bidirectional", True),
+                    context=package.get("context", 20))
         model.load_state_dict(package["state_dict"])
         return model
 

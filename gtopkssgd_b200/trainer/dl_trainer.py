@@ -263,8 +263,10 @@ class DLTrainer:
     def _synthetic_sizes(self):
         ntrain, ntest = SYNTHETIC_SIZES[self.dataset]
         if self.synthetic_train_size:
-            ntrain = int(self.synthetic_train_size)
+            ntrain = int(self.synthetic_train_size)  # in samples
             ntest = max(self.batch_size, min(ntest, ntrain // 5))
+            if self.dataset == "ptb":  # the PTB generator is sized in tokens
+                ntrain, ntest = ntrain * self.num_steps, max(ntest, 2 * self.batch_size) * self.num_steps
         return ntrain, ntest
 
     def imagenet_prepare(self):

@@ -1,0 +1,302 @@
+"""CPU tests of the framework layers: grouping, density schedule, compressor
+API, LR schedules, checkpoints + evaluate, log formats, models, data."""
+import math
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from gtopkssgd_b200 import settings
+from gtopkssgd_b200.models import create_net
+from gtopkssgd_b200.parallel.compression import TopKCompressor, compressors
+from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+from gtopkssgd_b200.parallel.flat_buffer import FlatBuffers, generate_groups
+
+
+def test_model_sizes_match_the_reference_table():
+    expected = {"resnet20": (269722, 59), "resnet56": (853018, 167), "resnet110": (1727962, 329),
+                "vgg16": (14728266, 54), "resnet50": (25557032, 161), "alexnet": (61100840, 16)}
+    for dnn, (numel, ntensors) in expected.items():
+        net, _ = create_net(1000 if dnn in ("resnet50", "alexnet") else 10, dnn)
+        ps = list(net.parameters())
+        assert (sum(p.numel() for p in ps), len(ps)) == (numel, ntensors), dnn
+    net, _ = create_net(10, "lstm", vocab_size=10000, batch_size=20)
+    assert sum(p.numel() for p in net.parameters()) == 66034000
+    net, ext = create_net(29, "lstman4")
+    assert sum(p.numel() for p in net.parameters()) == 27569568 and len(ext["labels"]) == 29
+
+
+def test_state_dict_keys_are_reference_compatible():
+    net, _ = create_net(10, "resnet20")
+    keys = set(net.state_dict())
+    for k in ("conv_1_3x3.weight", "bn_1.running_mean", "stage_1.0.conv_a.weight", "stage_3.2.bn_b.bias",
+              "classifier.weight"):
+        assert k in keys
+    net, _ = create_net(10, "vgg16")
+    assert {"features.0.weight", "features.1.running_var", "fc.bias"} <= set(net.state_dict())
+    net, _ = create_net(1000, "resnet50")
+    assert {"conv1.weight", "layer1.0.downsample.0.weight", "layer4.2.bn3.weight", "fc.weight"} <= set(net.state_dict())
+
+
+def test_grouping_by_threshold_backward_order():
+    names = ["a", "b", "c", "d", "e"]
+    sizes = dict(zip(names, [10, 20, 30, 40, 50]))
+    groups, key_group = generate_groups(names, sizes, 60)
+    assert groups == [["e", "d"], ["c", "b", "a"]]  # last layer first; a group closes once it holds >= 60
+    assert key_group == {"e": 0, "d": 0, "c": 1, "b": 1, "a": 1}
+    groups, _ = generate_groups(names, sizes, 640 * 1024 * 1024)
+    assert groups == [["e", "d", "c", "b", "a"]]  # default: the whole model is one group
+
+
+def test_flat_buffers_keep_views_and_values():
+    net, _ = create_net(10, "resnet20")
+    before = {n: p.detach().clone() for n, p in net.named_parameters()}
+    fb = FlatBuffers(net.named_parameters(), 100000)
+    assert len(fb.groups) == 3 and fb.numel == 269722
+    for n, p in net.named_parameters():
+        assert torch.equal(p, before[n])
+        s = fb.slots[n]
+        assert p.data_ptr() == fb.param.data_ptr() + 4 * s.offset
+    net(torch.randn(2, 3, 32, 32)).sum().backward()
+    assert float(fb.grad.abs().sum()) > 0
+    for p in net.parameters():
+        p.grad = None  # what zero_grad(set_to_none=True) does
+    assert fb.ensure_views() == 59
+
+
+def test_density_schedule_and_pin(monkeypatch):
+    net, _ = create_net(10, "mnistnet")
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+    monkeypatch.setattr(settings, "PIN_DENSITY", False)
+    d = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                             density=0.001)
+    assert d.get_current_density() == 0.004  # epoch 0
+    d.add_train_epoch()
+    assert d.get_current_density() == 0.001
+    d.stop()
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+    d = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                             density=0.001)
+    assert d.get_current_density() == 0.001
+    d.stop()
+
+
+def test_compressor_registry_api():
+    assert set(compressors) == {"topk", "topk2", "gtopk", "none"}
+    TopKCompressor.clear()
+    torch.manual_seed(0)
+    t = torch.randn(1000)
+    orig = t.clone()
+    out, idx = compressors["gtopk"].compress(t, "g0", ratio=0.01)
+    assert out is t and idx.numel() == 10
+    assert int((t != 0).sum()) == 10 and torch.equal(t[idx], orig[idx])
+    res = TopKCompressor.get_residuals("g0", t)
+    assert torch.allclose(res + t, orig)
+    # positions 0 and 1 of the selection were accepted globally, the rest returns to the residual
+    compressors["gtopk"].add_residuals(np.array([0, 1]), "g0")
+    back = idx[2:]
+    assert torch.allclose(res[back], orig[back]) and float(res[idx[:2]].abs().sum()) == 0
+    dense, ctx = compressors["none"].compress(t, "x", sigma_scale=2.5, ratio=0.5)
+    assert dense is t and ctx is None
+    TopKCompressor.clear()
+
+
+def test_gradient_accumulation_local_flag(monkeypatch):
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+    torch.manual_seed(0)
+    net, _ = create_net(10, "mnistnet")
+    net.eval()  # no dropout noise
+    opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
+    d = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                             density=0.01)
+    x = torch.randn(4, 1, 28, 28)
+    d.zero_grad()
+    d.local = True
+    net(x).sum().backward()
+    assert d._allreducer.allreduce_count == 0  # hooks skipped on the accumulation micro-step
+    d.local = False
+    net(x).sum().backward()
+    assert d._allreducer.allreduce_count == 1
+    d.step()
+    d.stop()
+
+
+def _tiny_trainer(tmp_path, monkeypatch, **kw):
+    from gtopkssgd_b200.trainer.dl_trainer import DLTrainer
+    monkeypatch.chdir(tmp_path)
+    args = dict(dist=False, ngpus=0, batch_size=4, data_dir="synthetic", dataset="cifar10", dnn="resnet20", lr=0.1,
+                nworkers=1, synthetic_train_size=64)
+    args.update(kw)
+    return DLTrainer(0, 1, **args)
+
+
+def test_lr_schedules(tmp_path, monkeypatch):
+    t = _tiny_trainer(tmp_path, monkeypatch, nworkers=4)
+    t.num_batches_per_epoch = 100
+    t.train_iter = 0
+    assert t.adjust_learning_rate(0, t.optimizer) == pytest.approx(0.1 / 4)  # warm-up starts at base_lr / P
+    t.train_iter = 500
+    assert t.adjust_learning_rate(5, t.optimizer) == pytest.approx(0.025 + 0.075 * 0.5)
+    for epoch, scale in ((10, 1.0), (80, 1.0), (81, 0.1), (121, 0.1), (122, 0.01), (155, 0.001)):
+        assert t.adjust_learning_rate(epoch, t.optimizer) == pytest.approx(0.1 * scale)
+    t.dataset = "imagenet"
+    for epoch, scale in ((29, 1.0), (30, 0.1), (60, 0.01), (80, 0.001)):
+        assert t.adjust_learning_rate(epoch, t.optimizer) == pytest.approx(0.1 * scale)
+    t.dnn = "lstm"
+    for epoch, scale in ((0, 1.0), (62, 1.0), (63, 0.01), (79, 0.01), (80, 0.001)):
+        assert t.adjust_learning_rate(epoch, t.optimizer) == pytest.approx(0.1 * scale)
+    t.dnn, t.lstman4_lr_epoch_tag, t.train_iter = "lstman4", 0, 100
+    t._set_lr(t.optimizer, 0.0003)
+    t.adjust_learning_rate(0, t.optimizer)
+    assert t.lr == pytest.approx(0.0003 / 1.01)
+
+
+def test_sgd_hyper_parameters_per_dataset(tmp_path, monkeypatch):
+    t = _tiny_trainer(tmp_path, monkeypatch)
+    g = t.optimizer.param_groups[0]
+    assert (g["momentum"], g["weight_decay"], g["nesterov"]) == (0.9, 1e-4, False)
+    t = _tiny_trainer(tmp_path, monkeypatch, dataset="ptb", dnn="lstm", batch_size=2, num_steps=5)
+    g = t.optimizer.param_groups[0]
+    assert (g["momentum"], g["weight_decay"]) == (0.0, 0.0)
+
+
+def test_checkpoint_roundtrip_and_evaluate(tmp_path, monkeypatch, caplog):
+    from gtopkssgd_b200.trainer import evaluate as ev
+    t = _tiny_trainer(tmp_path, monkeypatch, save_checkpoints=True, prefix="unit")
+    for _ in range(t.num_batches_per_epoch + 1):  # crosses one epoch boundary -> test() + checkpoint
+        t.optimizer.zero_grad()
+        t.train(1)
+        t.update_model()
+    path = os.path.join("weights", "unit", "resnet20-n1-bs4-lr0.1000", "resnet20-rank0-epoch0.pth")
+    assert os.path.isfile(path)
+    ckpt = torch.load(path, weights_only=False)
+    assert set(ckpt) == {"iter", "epoch", "state"} and ckpt["epoch"] == 0 and ckpt["iter"] == 16
+    # a dict shaped like the reference's loads into a fresh trainer
+    t2 = _tiny_trainer(tmp_path, monkeypatch)
+    t2.load_model_from_file(path)
+    assert t2.get_train_epoch() == 0 and t2.get_train_iter() == 16
+    for k, v in t2.net.state_dict().items():
+        assert torch.equal(v, ckpt["state"][k])
+    # evaluate.py parses dnn / batch size / lr from the directory name
+    os.rename(path, os.path.join(os.path.dirname(path), "resnet20-rank0-epoch1.pth"))
+    best = ev.evaluate(os.path.dirname(path), "resnet20", "cifar10", "synthetic", 1)
+    assert 0.0 <= best <= 1.0
+    assert ev.parse_model_dir("weights/x/resnet20-n4-bs32-lr0.1000") == ("resnet20", 32, 0.1)
+
+
+def test_log_lines_match_the_reference_parsers(tmp_path, monkeypatch):
+    """Regexes equivalent to the ones in scripts/*/plot_loss.py."""
+    import io
+    import logging
+    buf = io.StringIO()
+    h = logging.StreamHandler(buf)
+    h.setFormatter(settings.formatter)
+    settings.logger.addHandler(h)
+    try:
+        t = _tiny_trainer(tmp_path, monkeypatch)
+        for _ in range(t.num_batches_per_epoch + 1):
+            t.optimizer.zero_grad()
+            t.train(1)
+            t.update_model()
+        settings.logger.info("Time per iteration including communication: %f. Speed: %f images/s, current density: %f",
+                             0.5, 64.0, 0.001)
+    finally:
+        settings.logger.removeHandler(h)
+    text = buf.getvalue()
+    assert re.search(r"Epoch \d+, avg train acc: [\d.naN]+, lr: [\d.]+, avg loss: [\d.]+", text)
+    assert re.search(r"Epoch \d+, lr: [\d.]+, val loss: [\d.]+, val acc: [\d.]+", text)
+    assert re.search(r"Time per iteration including communication: [\d.]+. Speed: [\d.]+ images/s", text)
+    assert re.search(r"\d{4}-\d\d-\d\d .* \[dl_trainer.py:\d+\] INFO", text)
+
+
+def test_update_nworker_reshards(tmp_path, monkeypatch):
+    t = _tiny_trainer(tmp_path, monkeypatch, nworkers=1)
+    n1 = t.num_batches_per_epoch
+    t.update_nworker(2, 1)
+    assert t.nworkers == 2 and t.rank == 1 and t.num_batches_per_epoch == math.ceil(n1 / 2)
+    assert t.train_sampler.num_replicas == 2 and t.train_sampler.rank == 1
+    x, y = t.data_iter()
+    assert x.shape == (4, 3, 32, 32)
+
+
+def test_compat_functions_single_process():
+    from gtopkssgd_b200.parallel import compat
+    rng = np.random.RandomState(0)
+    dense = rng.randn(10000).astype(np.float32)
+    idx, vals = compat.topk(dense, 10)
+    assert np.all(np.abs(vals)[:-1] <= np.abs(vals)[1:])  # ascending magnitude, as the reference's utils.topk
+    v, i, inc = compat.gtopk_sparse_allreduce(None, vals, indexes=idx)
+    assert set(i.tolist()) == set(idx.tolist()) and len(inc) == 10
+    v1, i1, none = compat.topk_sparse_allreduce(None, vals, {}, indexes=idx)
+    assert none is None and len(v1) == 10
+    assert np.allclose(compat.dense_allreduce(None, dense), dense)
+
+
+def test_ptb_reader_windows(tmp_path):
+    from gtopkssgd_b200.data import ptb_reader
+    words = " ".join("w%d" % (i % 17) for i in range(400))
+    for part in ("train", "valid", "test"):
+        (tmp_path / ("ptb.%s.txt" % part)).write_text(" " + words + " \n " + words + " \n")
+    train, valid, test, w2i, i2w = ptb_reader.ptb_raw_data(str(tmp_path))
+    assert len(w2i) == 18 and "<eos>" in w2i
+    ds = ptb_reader.TrainDataset(train, batch_size=4, num_steps=5)
+    x, y = ds[3]
+    assert list(x[1:]) == list(y[:-1]) and len(ds) % 4 == 0
+
+
+def test_ctc_decoders_and_error_rates():
+    from gtopkssgd_b200.data.decoder import BeamCTCDecoder, GreedyDecoder, edit_distance
+    labels = "_'ABCDEFGHIJKLMNOPQRSTUVWXYZ "
+    dec = GreedyDecoder(labels)
+    assert edit_distance("kitten", "sitting") == 3
+    assert dec.wer("the cat sat", "the cat sat down") == 1 and dec.cer("abc d", "abd") == 1
+    # frames: H H _ I I ' ' T -> "HI T" after collapsing repeats and blanks
+    seq = [labels.index(c) for c in "HH_II T"]
+    probs = torch.full((1, len(seq), len(labels)), -5.0)
+    for t, c in enumerate(seq):
+        probs[0, t, c] = 5.0
+    strings, offsets = dec.decode(probs.softmax(-1), torch.tensor([len(seq)]))
+    assert strings[0][0] == "HI T" and offsets[0][0].tolist() == [0, 3, 5, 6]
+    beam = BeamCTCDecoder(labels, beam_width=8)
+    out, _ = beam.decode(probs.softmax(-1), torch.tensor([len(seq)]))
+    assert out[0][0] == "HI T"
+
+
+def test_audio_collate_and_bucketing():
+    from gtopkssgd_b200.data.audio import BucketingSampler, DistributedBucketingSampler, collate_spectrograms
+    from gtopkssgd_b200.data.synthetic import SyntheticAN4
+    ds = SyntheticAN4(20, 29, min_t=50, max_t=90)
+    batch = [ds[i] for i in range(4)]
+    inputs, targets, pct, sizes = collate_spectrograms(batch)
+    assert inputs.shape[:3] == (4, 1, 161) and inputs.shape[3] == max(b[0].size(1) for b in batch)
+    assert float(pct.max()) == 1.0 and int(sizes.sum()) == targets.numel()
+    assert len(BucketingSampler(ds, batch_size=8)) == 3
+    s0 = DistributedBucketingSampler(ds, batch_size=4, num_replicas=2, rank=0)
+    s1 = DistributedBucketingSampler(ds, batch_size=4, num_replicas=2, rank=1)
+    assert len(s0) == len(s1) == 3
+    seen = [tuple(b) for b in s0] + [tuple(b) for b in s1]
+    assert len(set(seen)) == 5  # 5 buckets, one repeated to even out the ranks
+
+
+def test_lstm_and_an4_models_train_one_step():
+    from gtopkssgd_b200.models.lstm import repackage_hidden
+    net, _ = create_net(10, "lstm", vocab_size=50, batch_size=3, num_steps=4)
+    net.embedding_dim  # noqa: B018
+    h = net.init_hidden()
+    x = torch.randint(0, 50, (4, 3))
+    small = type(net)(50, embedding_dim=16, num_steps=4, batch_size=3)
+    out, h2 = small(x, small.init_hidden())
+    assert out.shape == (4, 3, 50)
+    out.sum().backward()
+    assert all(t.grad_fn is None for t in repackage_hidden(h2))
+    del h
+    from gtopkssgd_b200.models.lstm_models import DeepSpeech
+    ds = DeepSpeech(labels="_ab ", rnn_hidden_size=16, nb_layers=2, bidirectional=False, context=3,
+                    audio_conf={"sample_rate": 16000, "window_size": 0.02})
+    y, lens = ds(torch.randn(2, 1, 161, 40), torch.tensor([40, 30]))
+    assert y.shape[0] == 2 and y.shape[2] == 4 and lens.tolist() == [20, 15]
+    pkg = DeepSpeech.serialize(ds, epoch=1)
+    ds2 = DeepSpeech.load_model_package(pkg)
+    assert pkg["epoch"] == 2 and set(ds2.state_dict()) == set(ds.state_dict())
