@@ -28,6 +28,7 @@ enum Status : uint32_t {
 constexpr int kHistBins = 2048;   // 11-bit first radix digit
 constexpr int kMaxRounds = 4;     // log2(16) recursive-doubling rounds
 constexpr int kMaxPeers = 16;
+constexpr int kTraceSlots = 64;
 
 // Per-rank control block.  The host clears it (one async memset) before every
 // launch that uses it, so every counter starts at zero.
@@ -44,6 +45,7 @@ struct Ctrl {
   unsigned int tie[kMaxRounds + 2];           // one tie counter per round
   unsigned int live[kMaxRounds + 2];
   unsigned int pad[64 - 16 - 3 * (kMaxRounds + 2)];
+  unsigned long long trace[kTraceSlots];      // %globaltimer stamps of CTA 0 at phase boundaries
   unsigned int hist[kMaxRounds + 2][3][kHistBins];  // radix histograms per round and pass
 };
 
@@ -52,6 +54,9 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+
+struct Ctrl;
+__device__ __forceinline__ void trace_stamp(Ctrl* c, int slot);
 
 __device__ __forceinline__ uint64_t ld_acquire_sys_u64(const uint64_t* p) {
   uint64_t v;
@@ -73,6 +78,11 @@ __device__ __forceinline__ unsigned int ld_relaxed_gpu_u32(const unsigned int* p
 }
 __device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Phase stamp for the device-side trace: thread 0 of the rank's CTA 0 only.
+__device__ __forceinline__ void trace_stamp(Ctrl* c, int slot) {
+  if (blockIdx.x == 0 && threadIdx.x == 0 && slot < kTraceSlots) c->trace[slot] = globaltimer_ns();
 }
 
 // Pair <-> 64-bit word, so that a pair always moves with one 8-byte access.

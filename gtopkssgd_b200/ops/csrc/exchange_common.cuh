@@ -59,13 +59,21 @@ __device__ __forceinline__ size_t flag_off(unsigned int parity, unsigned int whi
   return (size_t)parity * kFlagsPerParity + which;
 }
 
-// All CTAs of the rank copy n pairs to dst (peer or local memory).
+// All CTAs of the rank copy n pairs to dst (peer or local memory).  No fence
+// here: the caller passes the rank barrier and then one thread publishes the
+// data with a single system-scope release (release_flag), which is cumulative
+// over everything the barrier ordered before it.
 __device__ __forceinline__ void push_pairs(Pair* dst, const Pair* src, unsigned int n,
                                            unsigned int cta, unsigned int nct) {
   const unsigned int stride = nct * kSelThreads;
   for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride)
     st_pair(&dst[i], ld_pair_cg(&src[i]));
-  __threadfence_system();
+}
+
+// Publish: st.release.sys orders every store that happens-before it (this
+// thread's own and, through the preceding barrier, every other thread's).
+__device__ __forceinline__ void release_flag(uint64_t* flag, uint32_t epoch, uint32_t count) {
+  st_release_sys_u64(flag, ((uint64_t)epoch << 32) | (uint64_t)count);
 }
 
 // One thread per CTA waits for the flag, the CTA learns the count.

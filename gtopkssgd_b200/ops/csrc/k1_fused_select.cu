@@ -18,6 +18,7 @@
 //              entries of r and one collect pass.
 // The dense sparsified gradient of the reference is never materialised; the
 // output is k (int32 index, fp32 value) pairs in no particular order.
+#include <cstddef>
 #include "select_common.cuh"
 #include "host_api.h"
 
@@ -275,7 +276,9 @@ extern "C" int gtk_k1_select(const float* g, float* r, const float* g_scale, lon
     return GTK_ERR_ARG;
   const DeviceInfo* di = gtk_device_info();
   if (!di) return GTK_ERR_CUDA;
-  cudaError_t e = cudaMemsetAsync(ctrl, 0, sizeof(Ctrl), stream);
+  // header + trace + the two histogram sets K1 can touch
+  const size_t clear_bytes = offsetof(Ctrl, hist) + 2 * sizeof(((Ctrl*)0)->hist[0]);
+  cudaError_t e = cudaMemsetAsync(ctrl, 0, clear_bytes, stream);
   if (e != cudaSuccess) return GTK_ERR_CUDA;
   const long long nvec = d / 4;
   const long long tile = (long long)kK1Threads * kK1Vec;

@@ -16,6 +16,7 @@
 // when all ranks are emulated on one GPU for testing, in which case the launch
 // is cooperative so that all CTAs are co-resident and the flag waits make
 // progress.  gridDim.x CTAs serve each rank and meet in RankBarrier.
+#include <cstddef>
 #include "exchange_common.cuh"
 
 namespace gtk {
@@ -42,6 +43,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
 
   unsigned int rounds = 0;
   while ((1u << rounds) < P) ++rounds;
+  trace_stamp(ctrl, 0);
 
   for (unsigned int r = 0; r < rounds; ++r) {
     const unsigned int bit = 1u << r;
@@ -52,11 +54,10 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       Pair* dst = R.peer_slots[partner] + slot_off(parity, r, kcap);
       push_pairs(dst, cur, n_cur, cta, nct);
       if (!bar.sync(200 + r)) return;
-      if (cta == 0 && threadIdx.x == 0) {
-        __threadfence_system();
-        st_release_sys_u64(R.peer_flags[partner] + flag_off(parity, r),
-                           ((uint64_t)epoch << 32) | (uint64_t)n_cur);
-      }
+      trace_stamp(ctrl, 1 + 8 * r + 6);
+      if (cta == 0 && threadIdx.x == 0)
+        release_flag(R.peer_flags[partner] + flag_off(parity, r), epoch, n_cur);
+      trace_stamp(ctrl, 1 + 8 * r + 7);
       break;
     }
     if (low != 0u) break;  // already left the tree
@@ -71,16 +72,20 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       if (!cur_mapped) build_map(A, n_cur, R.map, d, cta, nct, ctrl);
     }
     unsigned int n_b = 0;
+    trace_stamp(ctrl, 1 + 8 * r + 0);
     if (!cta_wait_flag(sh, R.flags + flag_off(parity, r), epoch, ctrl, limit_ns, 210 + r, &n_b))
       return;
+    trace_stamp(ctrl, 1 + 8 * r + 1);
     if (n_b > kcap) {
       record_error(ctrl, ST_CAPACITY, 220 + r);
       n_b = kcap;
     }
     Pair* B = R.slots + slot_off(parity, r, kcap);
     if (!bar.sync(230 + r)) return;  // map complete
+    trace_stamp(ctrl, 1 + 8 * r + 2);
     probe_merge(A, n_cur, B, n_b, R.map, d, cta, nct, ctrl);
     if (!bar.sync(240 + r)) return;  // sums complete
+    trace_stamp(ctrl, 1 + 8 * r + 3);
     // ---- re-select the k largest magnitudes of A u live(B)
     const unsigned int n_a = n_cur;
     const unsigned int n_u = n_a + n_b;
@@ -91,6 +96,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     Threshold th;
     if (!radix_select_kth(sh.sel, bar, cta, nct, n_u, k, ctrl->hist[r], key_at, &th, 250 + 10 * r))
       return;
+    trace_stamp(ctrl, 1 + 8 * r + 4);
     Pair* OUT = R.work[cur_buf ^ 1];
     int32_t* map = R.map;
     auto on_placed = [&](Pair e, unsigned int pos) { map[e.idx] = (int32_t)pos; };
@@ -108,6 +114,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     }
     app.flush(on_placed);
     if (!bar.sync(290 + r)) return;  // OUT and its cursor complete
+    trace_stamp(ctrl, 1 + 8 * r + 5);
     n_cur = __ldcg(&ctrl->cursor[r]);
     if (n_cur > kcap) n_cur = kcap;
     cur_buf ^= 1;
@@ -126,12 +133,8 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       push_pairs(dst, cur, n_cur, cta, nct);
     }
     if (!bar.sync(400)) return;
-    if (cta == 0 && threadIdx.x == 0) {
-      __threadfence_system();
-      for (unsigned int q = 1; q < P; ++q)
-        st_release_sys_u64(R.peer_flags[q] + flag_off(parity, kFlagBcast),
-                           ((uint64_t)epoch << 32) | (uint64_t)n_cur);
-    }
+    if (cta == 0 && threadIdx.x < P && threadIdx.x > 0)  // one releasing thread per destination
+      release_flag(R.peer_flags[threadIdx.x] + flag_off(parity, kFlagBcast), epoch, n_cur);
   } else {
     if (!cta_wait_flag(sh, R.flags + flag_off(parity, kFlagBcast), epoch, ctrl, limit_ns, 410, &n_g))
       return;
@@ -141,10 +144,13 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     }
   }
   // ---- residual put-back of S_local \ S_global
+  trace_stamp(ctrl, 40);
   build_map(G, n_g, R.map, d, cta, nct, ctrl);
   if (!bar.sync(420)) return;
+  trace_stamp(ctrl, 41);
   put_back(R.sel, n_sel, G, n_g, R.map, R.resid, d, cta, nct);
   if (cta == 0 && threadIdx.x == 0) *R.n_global = n_g;
+  trace_stamp(ctrl, 42);
 }
 
 }  // namespace gtk
@@ -203,13 +209,16 @@ extern "C" int gtk_k2rank_fill(void* desc_host, const void* sel, const void* st,
 }
 
 static int k2_max_coresident(void* fn) {
+  static int cached = 0;  // the occupancy query costs microseconds; the answer never changes
+  if (cached) return cached;
   const DeviceInfo* di = gtk_device_info();
   if (!di) return 0;
   int occ = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)fn, kSelThreads, 0) !=
       cudaSuccess)
     return 0;
-  return occ * di->sms;
+  cached = occ * di->sms;
+  return cached;
 }
 
 // ranks_dev: device array of nranks_in_launch K2Rank descriptors (1 in production).
@@ -223,8 +232,11 @@ extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, uns
   if (k == 0 || k > kcap || nranks == 0 || nctas == 0) return GTK_ERR_ARG;
   const int maxco = k2_max_coresident((void*)k2_gtopk_exchange);
   if ((int)(nranks * nctas) > maxco) return GTK_ERR_ARG;
+  unsigned int rounds = 0;
+  while ((1u << rounds) < P) ++rounds;
+  const size_t clear_bytes = offsetof(Ctrl, hist) + (size_t)rounds * sizeof(((Ctrl*)0)->hist[0]);
   for (unsigned int i = 0; i < nranks; ++i)
-    if (cudaMemsetAsync(ctrl_dev[i], 0, sizeof(Ctrl), stream) != cudaSuccess) return GTK_ERR_CUDA;
+    if (cudaMemsetAsync(ctrl_dev[i], 0, clear_bytes, stream) != cudaSuccess) return GTK_ERR_CUDA;
   const K2Rank* ranks = (const K2Rank*)ranks_dev;
   void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &epoch, &limit_ns};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)k2_gtopk_exchange, dim3(nctas, nranks),

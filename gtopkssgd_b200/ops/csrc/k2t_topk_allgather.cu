@@ -37,14 +37,8 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
     push_pairs(dst, R.sel, n_sel, cta, nct);
   }
   if (!bar.sync(500)) return;
-  if (cta == 0 && threadIdx.x == 0) {
-    __threadfence_system();
-    for (unsigned int q = 0; q < P; ++q) {
-      if (q == me) continue;
-      st_release_sys_u64(R.peer_flags[q] + flag_off(parity, kFlagAg0 + me),
-                         ((uint64_t)epoch << 32) | (uint64_t)n_sel);
-    }
-  }
+  if (cta == 0 && threadIdx.x < P && threadIdx.x != me)  // one releasing thread per destination
+    release_flag(R.peer_flags[threadIdx.x] + flag_off(parity, kFlagAg0 + me), epoch, n_sel);
   // wait for every source
   unsigned int counts[kMaxPeers];
   for (unsigned int q = 0; q < P; ++q) {
@@ -156,9 +150,9 @@ extern "C" int gtk_k2t_allgather(const void* ranks_dev, void* const* ctrl_dev, u
   if (k == 0 || k > kcap || nranks == 0 || nctas == 0) return GTK_ERR_ARG;
   const DeviceInfo* di = gtk_device_info();
   if (!di) return GTK_ERR_CUDA;
-  int occ = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)k2t_topk_allgather,
-                                                    kSelThreads, 0) != cudaSuccess)
+  static int occ = 0;
+  if (!occ && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)k2t_topk_allgather,
+                                                            kSelThreads, 0) != cudaSuccess)
     return GTK_ERR_CUDA;
   if ((int)(nranks * nctas) > occ * di->sms) return GTK_ERR_ARG;
   for (unsigned int i = 0; i < nranks; ++i)

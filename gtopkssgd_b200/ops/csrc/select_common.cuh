@@ -45,9 +45,11 @@ __device__ __forceinline__ void smem_hist_flush(SelectShared& s, unsigned int* g
 // finds the digit D with count(bins > D) < k_rem <= count(bins >= D).
 // Results are left in shared memory: res_digit, res_krem (k_rem minus the count
 // above D), res_total (all entries), res_equal (count in bin D).
+// With local = true the counts are read from the CTA's own shared histogram
+// (single-CTA ranks never touch the global copy).
 template <int NBINS>
 __device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* ghist,
-                                           unsigned int k_rem) {
+                                           unsigned int k_rem, bool local) {
   constexpr int BPT = NBINS / kSelThreads;
   static_assert(BPT >= 1, "bins per thread");
   const int t = threadIdx.x;
@@ -55,7 +57,7 @@ __device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* 
   unsigned int mine = 0;
 #pragma unroll
   for (int j = 0; j < BPT; ++j) {
-    c[j] = __ldcg(&ghist[t * BPT + j]);
+    c[j] = local ? s.hist[t * BPT + j] : __ldcg(&ghist[t * BPT + j]);
     mine += c[j];
   }
   // inclusive suffix sum over threads (higher thread = higher bins)
@@ -111,9 +113,10 @@ __device__ __forceinline__ bool radix_select_kth(SelectShared& s, RankBarrier& b
     const uint32_t key = key_at(i);
     if (key != 0xffffffffu) atomicAdd(&s.hist[key >> 20], 1u);
   }
-  smem_hist_flush(s, hist[0], kHistBins);
+  const bool local = nctas == 1;
+  if (!local) smem_hist_flush(s, hist[0], kHistBins);
   if (!bar.sync(where + 0)) return false;
-  find_digit<kHistBins>(s, hist[0], k_rem);
+  find_digit<kHistBins>(s, hist[0], k_rem, local);
   if (s.res_total <= k) {  // not more live entries than k: keep them all
     out->key = 0u;
     out->quota = 0u;
@@ -130,9 +133,9 @@ __device__ __forceinline__ bool radix_select_kth(SelectShared& s, RankBarrier& b
     const uint32_t key = key_at(i);
     if (key != 0xffffffffu && (key >> 20) == prefix) atomicAdd(&s.hist[(key >> 10) & 1023u], 1u);
   }
-  smem_hist_flush(s, hist[1], 1024);
+  if (!local) smem_hist_flush(s, hist[1], 1024);
   if (!bar.sync(where + 1)) return false;
-  find_digit<1024>(s, hist[1], k_rem);
+  find_digit<1024>(s, hist[1], k_rem, local);
   prefix = (prefix << 10) | s.res_digit;
   k_rem = s.res_krem;
   __syncthreads();
@@ -142,9 +145,9 @@ __device__ __forceinline__ bool radix_select_kth(SelectShared& s, RankBarrier& b
     const uint32_t key = key_at(i);
     if (key != 0xffffffffu && (key >> 10) == prefix) atomicAdd(&s.hist[key & 1023u], 1u);
   }
-  smem_hist_flush(s, hist[2], 1024);
+  if (!local) smem_hist_flush(s, hist[2], 1024);
   if (!bar.sync(where + 2)) return false;
-  find_digit<1024>(s, hist[2], k_rem);
+  find_digit<1024>(s, hist[2], k_rem, local);
   out->key = (prefix << 10) | s.res_digit;
   out->quota = s.res_krem;
   out->select_all = false;

@@ -30,6 +30,17 @@ STATUS_NAMES = {
 
 # Ctrl header words (uint32) -- see csrc/common.cuh
 CTRL_BAR, CTRL_ABORT, CTRL_STATUS, CTRL_WHERE, CTRL_NOUT = 0, 1, 2, 3, 4
+CTRL_TRACE_OFFSET_WORDS, CTRL_TRACE_SLOTS = 64, 64  # u64 stamps start after the 256-byte header
+
+
+def read_trace(ctrl) -> dict:
+    """Device-side phase stamps of the last launch that used this control
+    block: {slot: nanoseconds since slot 0}.  Slots that were not reached are
+    omitted.  Synchronises."""
+    import torch
+    raw = ctrl[CTRL_TRACE_OFFSET_WORDS:CTRL_TRACE_OFFSET_WORDS + 2 * CTRL_TRACE_SLOTS].cpu().view(torch.int64)
+    t0 = int(raw[0])
+    return {i: int(v) - t0 for i, v in enumerate(raw.tolist()) if v != 0}
 
 
 class GtopkNativeError(RuntimeError):
