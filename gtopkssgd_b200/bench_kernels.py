@@ -31,7 +31,11 @@ class _Timer:
     def __init__(self, flush: bool):
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
 
-    def time(self, fn, iters=10, warmup=3, setup=None):
+    iters, warmup = 10, 3
+
+    def time(self, fn, iters=None, warmup=None, setup=None):
+        iters = iters or _Timer.iters
+        warmup = _Timer.warmup if warmup is None else warmup
         for _ in range(warmup):
             if setup:
                 setup()
@@ -136,7 +140,7 @@ def bench_k2_emulated(d: int, rho: float, world: int, nctas=None):
         epoch[0] += 1
         ex.launch_gtopk(ranks, desc, 0, world, k, epoch[0], nctas=nctas)
 
-    med, best = _Timer(False).time(fn, iters=20)
+    med, best = _Timer(False).time(fn, iters=2 * _Timer.iters)
     bad = [r.status() for r in ranks if r.status() != (0, 0)]
     return {"kernel": "k2_gtopk_exchange(emulated)", "d": d, "rho": rho, "k": k, "P": world,
             "nctas": nctas or ex.default_nctas(k, world), "us": med * 1e6, "best_us": best * 1e6, "errors": bad}
@@ -149,22 +153,30 @@ def main():
     ap.add_argument("--k2-sizes", type=float, nargs="*", default=[0.27, 14.7, 25.6, 66])
     ap.add_argument("--worlds", type=int, nargs="*", default=[2, 4, 8])
     ap.add_argument("--json", type=str, default=None)
+    ap.add_argument("--only", type=str, nargs="*", default=["k1", "k3", "k4", "k2"],
+                    help="which kernels to run (a small selection keeps a profiler capture short)")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
+    _Timer.iters, _Timer.warmup = args.iters, args.warmup
     peak = _peak_gbs()
     rows = []
     for m in args.sizes:
         d = int(m * 1e6)
         flush = d * 4 < (160 << 20)
-        for rho in args.densities:
-            rows.append(bench_k1(d, rho, peak, flush))
+        if "k1" in args.only:
+            for rho in args.densities:
+                rows.append(bench_k1(d, rho, peak, flush))
+                print(json.dumps(rows[-1]), flush=True)
+        if "k3" in args.only:
+            for row in bench_k3(d, peak, flush):
+                rows.append(row)
+                print(json.dumps(row), flush=True)
+        if "k4" in args.only:
+            rows.append(bench_k4(d, peak, flush))
             print(json.dumps(rows[-1]), flush=True)
-        for row in bench_k3(d, peak, flush):
-            rows.append(row)
-            print(json.dumps(row), flush=True)
-        rows.append(bench_k4(d, peak, flush))
-        print(json.dumps(rows[-1]), flush=True)
         torch.cuda.empty_cache()
-    for m in args.k2_sizes:
+    for m in (args.k2_sizes if "k2" in args.only else []):
         d = int(m * 1e6)
         for world in args.worlds:
             rows.append(bench_k2_emulated(d, 0.001, world))
