@@ -4,6 +4,9 @@ initialisation and reference-compatible ``state_dict`` keys."""
 from __future__ import annotations
 
 from .alexnet import AlexNet
+from .cifar_extras import (caffe_cifar, densenet100_12, preresnet20, preresnet32, preresnet44, preresnet56,
+                           preresnet110, resnet_mod20, resnet_mod32, resnet_mod44, resnet_mod56, resnet_mod110,
+                           resnext29_8_64, resnext29_16_64)
 from .imagenet_resnet import resnet18, resnet34, resnet50, resnet101, resnet152
 from .lstm import lstm, repackage_hidden
 from .lstman4 import create_net as LSTMAN4
@@ -22,6 +25,10 @@ def create_net(num_classes: int, dnn: str = "resnet20", **kwargs):
     if dnn in ("resnet20", "resnet32", "resnet44", "resnet56", "resnet110"):
         net = globals()[dnn](num_classes=num_classes)
     elif dnn in ("resnet18", "resnet34", "resnet50", "resnet101", "resnet152"):
+        net = globals()[dnn](num_classes=num_classes)
+    elif dnn in ("preresnet20", "preresnet32", "preresnet44", "preresnet56", "preresnet110", "resnet_mod20",
+                 "resnet_mod32", "resnet_mod44", "resnet_mod56", "resnet_mod110", "resnext29_8_64",
+                 "resnext29_16_64", "densenet100_12", "caffe_cifar"):
         net = globals()[dnn](num_classes=num_classes)
     elif dnn == "mnistnet":
         net = MnistNet()

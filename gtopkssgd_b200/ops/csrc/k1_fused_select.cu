@@ -52,6 +52,9 @@ k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __res
           const K1State* __restrict__ st, Pair* __restrict__ cand, unsigned int cap, Ctrl* ctrl,
           long long d) {
   __shared__ Pair wstage[kK1Threads / 32][kWarpStage];
+  __shared__ unsigned int shist[kHistBins];  // first radix digit of every candidate of this CTA
+  for (int i = threadIdx.x; i < kHistBins; i += kK1Threads) shist[i] = 0u;
+  __syncthreads();
   Pair* wbuf = wstage[threadIdx.x >> 5];
   unsigned int wcnt = 0;
   const float tau = st->tau;
@@ -114,6 +117,7 @@ k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __res
               p.idx = (int32_t)(head + (v << 2) + e);
               p.val = a[e];
               wbuf[wcnt + __popc(m & lanemask_lt())] = p;
+              atomicAdd(&shist[mag_key(a[e]) >> 20], 1u);
             }
             wcnt += __popc(m);
             if (wcnt > (unsigned int)kWarpFlushAt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
@@ -143,6 +147,7 @@ k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __res
           p.idx = (int32_t)i;
           p.val = a;
           wbuf[wcnt + __popc(m & lanemask_lt())] = p;
+          atomicAdd(&shist[mag_key(a) >> 20], 1u);
         }
         wcnt += __popc(m);
         if (wcnt > (unsigned int)kWarpFlushAt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
@@ -150,6 +155,12 @@ k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __res
     }
   }
   if (wcnt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
+  // publish this CTA's part of the first-pass histogram (k1_finish starts from it)
+  __syncthreads();
+  for (int i = threadIdx.x; i < kHistBins; i += kK1Threads) {
+    const unsigned int c = shist[i];
+    if (c) atomicAdd(&ctrl->hist[0][0][i], c);
+  }
 }
 
 // Re-predict tau so that the next stream pass yields about target_ratio * k
@@ -179,13 +190,14 @@ k1_finish(float* __restrict__ r, long long d, Pair* __restrict__ cand, unsigned 
   auto none = [](Pair, unsigned int) {};
 
   if (!exact_mode) {
-    unsigned int nct = (C + 4095u) / 4096u;
+    unsigned int nct = (C + 1023u) / 1024u;  // one or two candidates per thread and pass
     if (nct < 1u) nct = 1u;
     if (nct > gridDim.x) nct = gridDim.x;
     if (blockIdx.x >= nct) return;
     RankBarrier bar{ctrl, nct, 0u, limit_ns};
     auto key_at = [&](unsigned int i) -> uint32_t { return mag_key(cand[i].val); };
-    if (!radix_select_kth(s, bar, blockIdx.x, nct, C, k, ctrl->hist[0], key_at, &th, 100)) return;
+    if (!radix_select_kth(s, bar, blockIdx.x, nct, C, k, ctrl->hist[0], key_at, &th, 100, true))
+      return;
     StagedAppender app{&s, sel, &ctrl->cursor[0], k, ctrl};
     app.begin();
     const unsigned int stride = nct * kSelThreads;

@@ -98,25 +98,30 @@ __device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* 
 // Radix select of the k-th largest magnitude over `n` logical entries, where
 // key_at(i) returns the 31-bit magnitude key of entry i, or 0xffffffff for a dead
 // entry.  hist points to three zeroed global histograms [3][kHistBins].
+// have_pass0: hist[0] already holds the complete first-digit histogram of the
+// entries (an earlier kernel built it), so the first sweep is skipped.
 // Returns false on abort.
 template <typename KeyAt>
 __device__ __forceinline__ bool radix_select_kth(SelectShared& s, RankBarrier& bar, unsigned int cta,
                                                  unsigned int nctas, unsigned int n, unsigned int k,
                                                  unsigned int (*hist)[kHistBins], KeyAt key_at,
-                                                 Threshold* out, uint32_t where) {
+                                                 Threshold* out, uint32_t where,
+                                                 bool have_pass0 = false) {
   const unsigned int stride = nctas * kSelThreads;
   uint32_t prefix = 0;
   unsigned int k_rem = k;
-  // pass 0: bits 30..20
-  smem_hist_clear(s);
-  for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride) {
-    const uint32_t key = key_at(i);
-    if (key != 0xffffffffu) atomicAdd(&s.hist[key >> 20], 1u);
-  }
   const bool local = nctas == 1;
-  if (!local) smem_hist_flush(s, hist[0], kHistBins);
-  if (!bar.sync(where + 0)) return false;
-  find_digit<kHistBins>(s, hist[0], k_rem, local);
+  // pass 0: bits 30..20
+  if (!have_pass0) {
+    smem_hist_clear(s);
+    for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride) {
+      const uint32_t key = key_at(i);
+      if (key != 0xffffffffu) atomicAdd(&s.hist[key >> 20], 1u);
+    }
+    if (!local) smem_hist_flush(s, hist[0], kHistBins);
+    if (!bar.sync(where + 0)) return false;
+  }
+  find_digit<kHistBins>(s, hist[0], k_rem, local && !have_pass0);
   if (s.res_total <= k) {  // not more live entries than k: keep them all
     out->key = 0u;
     out->quota = 0u;

@@ -300,3 +300,43 @@ def test_lstm_and_an4_models_train_one_step():
     pkg = DeepSpeech.serialize(ds, epoch=1)
     ds2 = DeepSpeech.load_model_package(pkg)
     assert pkg["epoch"] == 2 and set(ds2.state_dict()) == set(ds.state_dict())
+
+
+def test_cost_models_and_simulator():
+    from gtopkssgd_b200.analysis import cost_models as cm
+    m, rho = 25 * 1024 * 1024, 0.001
+    assert cm.gtopk_allreduce_ms(32, m, rho) < cm.topk_allreduce_ms(32, m, rho) < cm.dense_allreduce_ms(32, m)
+    assert cm.gtopk_allreduce_ms(4, m, rho) > cm.topk_allreduce_ms(4, m, rho)  # the tree only pays off at scale
+    eff = cm.scaling_efficiency(cm.PUBLISHED_THROUGHPUT["ResNet-50"]["gtopk"])
+    assert eff[-1] == pytest.approx(100 * 39.119 / 52.873)
+    assert cm.speedup_over(cm.PUBLISHED_THROUGHPUT["VGG-16"]["gtopk"],
+                           cm.PUBLISHED_THROUGHPUT["VGG-16"]["dense"])[-1] == pytest.approx(9.78, abs=0.01)
+    assert sum(cm.breakdown_ratios("AlexNet")) == pytest.approx(1.0)
+    # three layers whose all-reduce is latency dominated: merging must not be slower than plain WFBP,
+    # and both beat a single all-reduce after backward only when overlap exists
+    sim = cm.Simulator("toy", computes=[100.0, 100.0, 100.0], sizes=[1000, 1000, 1000], num_of_nodes=8)
+    plain, merged, single = sim.wfbp(), sim.mg_wfbp(), sim.single_allreduce()
+    assert merged.total_ms <= plain.total_ms + 1e-9
+    assert single.total_ms * 1000 == pytest.approx(300.0 + cm.ring_allreduce_us(8, 3000))
+    assert len(plain.comm) == 3 and plain.comm[0][0] == 100.0
+
+
+def test_log_parser_reads_trainer_lines(tmp_path):
+    from gtopkssgd_b200.analysis.log_parser import mean_speed, parse_log
+    text = "\n".join([
+        "2026-01-01 10:00:00,123 [dl_trainer.py:142] INFO num_batches_per_epoch: 391",
+        "2026-01-01 10:05:00,000 [dl_trainer.py:300] INFO Epoch 1, avg train acc: 35.500000, lr: 0.100000, avg loss: 1.750000",
+        "2026-01-01 10:05:10,000 [dl_trainer.py:420] INFO Epoch 0, lr: 0.100000, val loss: 1.600000, val acc: 0.412000",
+        "2026-01-01 10:06:00,000 [gtopk_trainer.py:120] INFO Time per iteration including communication: 0.050000. "
+        "Speed: 640.000000 images/s, current density: 0.001000",
+        "2026-01-01 10:07:00,000 [allreducer.py:330] INFO [rank:0]cla...ght[269722]: 0.0,0.0,0.000120,0.000250,0.0,0.0,0.0",
+        "2026-01-01 10:10:00,000 [dl_trainer.py:300] INFO Epoch 2, avg train acc: 48.000000, lr: 0.100000, avg loss: 1.400000",
+    ])
+    p = tmp_path / "run.log"
+    p.write_text(text + "\n")
+    log = parse_log(str(p))
+    assert log.num_batches_per_epoch == 391 and log.epochs == [1, 2]
+    assert log.train_loss == [1.75, 1.4] and log.times_s == [0, 300]
+    assert log.val_acc == [0.412] and log.densities == [0.001]
+    assert mean_speed(log, skip=0) == 640.0
+    assert log.profiling[0]["compression"] == pytest.approx(1.2e-4) and log.profiling[0]["size"] == 269722
