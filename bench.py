@@ -64,6 +64,8 @@ def main():
     ap.add_argument("--threshold", type=int, default=None, help="merge threshold in elements (default: one group)")
     ap.add_argument("--channels-last", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="run every iteration eagerly instead of replaying the captured whole-iteration graph")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -102,7 +104,7 @@ def main():
     sparse = args.compressor != "none"
     trainer = DLTrainer(rank, world, dist=False, batch_size=bs, is_weak_scaling=True, ngpus=1, data_dir="synthetic",
                         dataset=dataset, dnn=args.model, lr=lr, nworkers=world, device=device,
-                        synthetic_train_size=max(4096, bs * world * 64))
+                        synthetic_train_size=max(4096, bs * world * 64), cuda_graph=not args.no_cuda_graph)
     if args.channels_last and args.model not in ("lstm",):
         trainer.net.to(memory_format=torch.channels_last)
     comm.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
@@ -124,20 +126,14 @@ def main():
         dev_x = dev_x.contiguous(memory_format=torch.channels_last)
     hidden = net.init_hidden() if is_lstm else None
 
+    from gtopkssgd_b200.trainer.graphed_step import GraphedStep
+    clip = 0.25 if is_lstm else None
+    stepper = GraphedStep(trainer, clip_norm=clip, warmup=3 if not args.no_cuda_graph else 1 << 60)
+
     def device_step():
+        # kernel-only arm: same iteration as DLTrainer.train_step, batch already on the device
         nonlocal hidden
-        optimizer.zero_grad()
-        if is_lstm:
-            from gtopkssgd_b200.models.lstm import repackage_hidden
-            hidden = repackage_hidden(hidden)
-            out, hidden = net(dev_x, hidden)
-            loss = crit(out.view(-1, net.vocab_size), dev_y.reshape(-1))
-        else:
-            loss = crit(net(dev_x), dev_y)
-        loss.backward()
-        if is_lstm:
-            optimizer.clip_grad_norm(0.25)
-        optimizer.step()
+        loss, _, hidden = stepper.run(dev_x, dev_y, hidden)
         return loss
 
     e2e_state = {"hidden": net.init_hidden() if is_lstm else None, "i": 0}
@@ -145,13 +141,7 @@ def main():
     def e2e_step():
         batch = host_batches[e2e_state["i"] % len(host_batches)]
         e2e_state["i"] += 1
-        optimizer.zero_grad()
-        if is_lstm:
-            _, e2e_state["hidden"] = trainer.train(1, data=batch, hidden=e2e_state["hidden"])
-            optimizer.clip_grad_norm(0.25)
-        else:
-            trainer.train(1, data=batch)
-        trainer.update_model()
+        e2e_state["hidden"] = trainer.train_step(data=batch, hidden=e2e_state["hidden"], clip_norm=clip)
         return trainer.loss  # device -> host read of this step's loss
 
     def timed(fn, steps):
@@ -196,6 +186,16 @@ def main():
     # ---- per-iteration communication time: select (K1) and exchange (K2 + put-back), device-timed
     comm_ms = {}
     a = optimizer._allreducer
+    # timed eagerly: CUDA-event timers cannot live inside a replayed graph
+    a.timers.enabled = True
+    for e in a.engines:
+        a.timers.means(e.g.key)
+    for _ in range(5):
+        if hidden is not None:
+            from gtopkssgd_b200.models.lstm import repackage_hidden
+            hidden = repackage_hidden(hidden)
+        _, _, hidden = stepper._iteration(dev_x, dev_y, hidden)
+    torch.cuda.synchronize()
     for e in a.engines:
         m = a.timers.means(e.g.key)
         comm_ms = {"select_ms": m["compression"] * 1e3, "exchange_ms": m["allreduce"] * 1e3}
@@ -215,6 +215,7 @@ def main():
                    "optimizer": "momentum SGD (fused flat-buffer step)",
                    "l2": "inputs larger than L2 (activations and gradients exceed 126 MB per step); no flush",
                    "merge_groups": len(a.engines), "channels_last": bool(args.channels_last),
+                   "cuda_graph": not args.no_cuda_graph,
                    "tf32": False},
         "comm_ms_per_iter": comm_ms,
         "select_stats": sel_stats,

@@ -85,15 +85,12 @@ def run_config(d, rho, iters=10, warmup=3, with_dense=True, with_rehost=True):
     if world > 1:
         region = ex.SymmetricRegion.create_ipc(ex.region_bytes(k, False), group=comm.cpu_group())
         rc = ex.ExchangeRank(rank, world, d, k, sel, resid, region)
-    epoch = [0]
-
     def k1():
         sel.select(grads[it[0] & 1], resid, k)
         it[0] += 1
 
     def k2():
-        epoch[0] += 1
-        ex.launch_gtopk([rc], rc.desc, rank, world, k, epoch[0], limit_ms=10000)
+        ex.launch_gtopk([rc], rc.desc, rank, world, k, limit_ms=10000)
 
     def both():
         k1()

@@ -35,14 +35,19 @@ class ClipNorm:
                                              current_stream_handle(self.device))
         _lib.check(code, "gtk_k4_sumsq_dense")
 
-    def add_pairs(self, pairs: torch.Tensor, counts: torch.Tensor, nseg: int, seg_stride: int) -> None:
+    def add_pairs(self, pairs: torch.Tensor, counts: torch.Tensor, nseg: int, seg_stride: int,
+                  parity_word=None, parity_stride: int = 0) -> None:
         if not self.is_cuda:
+            if parity_word is not None:
+                pairs = pairs[((int(parity_word) - 1) & 1) * parity_stride:]
             for s in range(nseg):
                 _, val = pairs_to_tensors(pairs[s * seg_stride:(s + 1) * seg_stride], int(counts[s]))
                 self._cpu_sumsq += float(val.double().pow(2).sum())
             return
         code = _lib.lib().gtk_k4_sumsq_pairs(pairs.data_ptr(), counts.data_ptr(), nseg, seg_stride,
-                                             self.state.data_ptr(), current_stream_handle(self.device))
+                                             self.state.data_ptr(),
+                                             None if parity_word is None else parity_word.data_ptr(),
+                                             int(parity_stride), current_stream_handle(self.device))
         _lib.check(code, "gtk_k4_sumsq_pairs")
 
     def finalize(self, max_norm: float, scale: float = 1.0) -> torch.Tensor:

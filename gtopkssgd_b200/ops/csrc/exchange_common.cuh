@@ -36,6 +36,8 @@ struct K2Rank {
   uint64_t* flags;
   Ctrl* ctrl;
   unsigned int* n_global; // device word: number of pairs in gout[parity]
+  unsigned int* epoch;    // device word: call counter (starts at 1); the kernel reads it at entry and
+                          // adds one after its last barrier, so a replayed CUDA graph needs no new argument
   Pair* peer_slots[kMaxPeers];
   Pair* peer_ag[kMaxPeers];
   Pair* peer_gout[kMaxPeers];

@@ -23,10 +23,10 @@ namespace gtk {
 
 __global__ void __launch_bounds__(kSelThreads)
 k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsigned int P,
-                  unsigned int k, unsigned int kcap, unsigned int d, unsigned int epoch,
-                  unsigned long long limit_ns) {
+                  unsigned int k, unsigned int kcap, unsigned int d, unsigned long long limit_ns) {
   __shared__ ExchangeShared sh;
   const K2Rank& R = ranks[blockIdx.y];
+  const unsigned int epoch = __ldcg(R.epoch);  // every CTA reads it before its first barrier
   const unsigned int me = rank_base + blockIdx.y;
   const unsigned int cta = blockIdx.x, nct = gridDim.x;
   const unsigned int parity = epoch & 1u;
@@ -149,7 +149,10 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
   if (!bar.sync(420)) return;
   trace_stamp(ctrl, 41);
   put_back(R.sel, n_sel, G, n_g, R.map, R.resid, d, cta, nct);
-  if (cta == 0 && threadIdx.x == 0) *R.n_global = n_g;
+  if (cta == 0 && threadIdx.x == 0) {
+    *R.n_global = n_g;
+    *R.epoch = epoch + 1u;  // safe: all CTAs passed the barrier above, hence read the old value
+  }
   trace_stamp(ctrl, 42);
 }
 
@@ -179,8 +182,8 @@ extern "C" void gtk_symm_layout(unsigned int kcap, int with_allgather, unsigned 
 // Fill one K2Rank descriptor on the host (the caller copies it to the device).
 extern "C" int gtk_k2rank_fill(void* desc_host, const void* sel, const void* st, void* work0,
                                void* work1, void* map, void* resid, void* symm_local, void* ctrl,
-                               void* n_global, unsigned int kcap, int with_allgather,
-                               unsigned int P, void* const* symm_peers) {
+                               void* n_global, void* epoch_word, unsigned int kcap,
+                               int with_allgather, unsigned int P, void* const* symm_peers) {
   if (P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
   unsigned long long lay[5];
   gtk_symm_layout(kcap, with_allgather, lay);
@@ -198,6 +201,7 @@ extern "C" int gtk_k2rank_fill(void* desc_host, const void* sel, const void* st,
   r->flags = (uint64_t*)(base + lay[3]);
   r->ctrl = (Ctrl*)ctrl;
   r->n_global = (unsigned int*)n_global;
+  r->epoch = (unsigned int*)epoch_word;
   for (unsigned int q = 0; q < (unsigned int)kMaxPeers; ++q) {
     char* pb = q < P ? (char*)symm_peers[q] : nullptr;
     r->peer_slots[q] = pb ? (Pair*)(pb + lay[0]) : nullptr;
@@ -225,8 +229,8 @@ static int k2_max_coresident(void* fn) {
 // ctrl_dev[i]: control block of each of those ranks (cleared here).
 extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, unsigned int nranks,
                                unsigned int rank_base, unsigned int P, unsigned int k,
-                               unsigned int kcap, unsigned int d, unsigned int epoch,
-                               unsigned int nctas, unsigned long long limit_ns, void* stream_) {
+                               unsigned int kcap, unsigned int d, unsigned int nctas,
+                               unsigned long long limit_ns, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (P < 2 || (P & (P - 1)) != 0 || P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
   if (k == 0 || k > kcap || nranks == 0 || nctas == 0) return GTK_ERR_ARG;
@@ -238,7 +242,7 @@ extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, uns
   for (unsigned int i = 0; i < nranks; ++i)
     if (cudaMemsetAsync(ctrl_dev[i], 0, clear_bytes, stream) != cudaSuccess) return GTK_ERR_CUDA;
   const K2Rank* ranks = (const K2Rank*)ranks_dev;
-  void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &epoch, &limit_ns};
+  void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &limit_ns};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)k2_gtopk_exchange, dim3(nctas, nranks),
                                               dim3(kSelThreads), args, 0, stream);
   gtk_count_launch(1);

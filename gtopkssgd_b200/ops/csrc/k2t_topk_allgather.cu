@@ -17,10 +17,11 @@ namespace gtk {
 __global__ void __launch_bounds__(kSelThreads)
 k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsigned int P,
                    unsigned int k, unsigned int kcap, unsigned int work_cap, unsigned int d,
-                   unsigned int epoch, int reselect, unsigned int* __restrict__ seg_counts_all,
+                   int reselect, unsigned int* __restrict__ seg_counts_all,
                    unsigned long long limit_ns) {
   __shared__ ExchangeShared sh;
   const K2Rank& R = ranks[blockIdx.y];
+  const unsigned int epoch = __ldcg(R.epoch);
   const unsigned int me = rank_base + blockIdx.y;
   const unsigned int cta = blockIdx.x, nct = gridDim.x;
   const unsigned int parity = epoch & 1u;
@@ -55,7 +56,11 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
     counts[q] = c;
   }
   if (cta == 0 && threadIdx.x < P) seg_counts[threadIdx.x] = counts[threadIdx.x];
-  if (!reselect) return;
+  if (!reselect) {
+    if (!bar.sync(535)) return;  // every CTA has read the epoch word
+    if (cta == 0 && threadIdx.x == 0) *R.epoch = epoch + 1u;
+    return;
+  }
 
   // ---- topk2: merge the P lists in rank order, then keep the k largest sums
   Pair* A = R.work[0];
@@ -133,7 +138,10 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
   unsigned int n_g = __ldcg(&ctrl->cursor[0]);
   if (n_g > kcap) n_g = kcap;
   put_back(R.sel, n_sel, G, n_g, R.map, R.resid, d, cta, nct);
-  if (cta == 0 && threadIdx.x == 0) *R.n_global = n_g;
+  if (cta == 0 && threadIdx.x == 0) {
+    *R.n_global = n_g;
+    *R.epoch = epoch + 1u;
+  }
 }
 
 }  // namespace gtk
@@ -143,7 +151,7 @@ using namespace gtk;
 extern "C" int gtk_k2t_allgather(const void* ranks_dev, void* const* ctrl_dev, unsigned int nranks,
                                  unsigned int rank_base, unsigned int P, unsigned int k,
                                  unsigned int kcap, unsigned int work_cap, unsigned int d,
-                                 unsigned int epoch, int reselect, void* seg_counts,
+                                 int reselect, void* seg_counts,
                                  unsigned int nctas, unsigned long long limit_ns, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (P < 2 || P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
@@ -159,8 +167,7 @@ extern "C" int gtk_k2t_allgather(const void* ranks_dev, void* const* ctrl_dev, u
     if (cudaMemsetAsync(ctrl_dev[i], 0, sizeof(Ctrl), stream) != cudaSuccess) return GTK_ERR_CUDA;
   const K2Rank* ranks = (const K2Rank*)ranks_dev;
   unsigned int* segc = (unsigned int*)seg_counts;
-  void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &work_cap, &d, &epoch, &reselect, &segc,
-                  &limit_ns};
+  void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &work_cap, &d, &reselect, &segc, &limit_ns};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)k2t_topk_allgather, dim3(nctas, nranks),
                                               dim3(kSelThreads), args, 0, stream);
   gtk_count_launch(1);

@@ -21,7 +21,17 @@ namespace gtk {
 
 constexpr int kK3Threads = 512;
 
+// Sparse inputs may live in a two-parity buffer written by the exchange kernel:
+// the segment base is pairs + ((*parity_word - 1) & 1) * parity_stride, where
+// parity_word is the exchange's call counter after the call (nullptr: no offset).
+__device__ __forceinline__ const Pair* parity_base(const Pair* pairs, const unsigned int* parity_word,
+                                                   unsigned int parity_stride) {
+  if (!parity_word) return pairs;
+  return pairs + (size_t)((*parity_word - 1u) & 1u) * parity_stride;
+}
+
 struct SgdHyper {
+  const float* lr_ptr;  // device-resident learning rate (read when non-null; lets a captured graph follow a schedule)
   float lr;
   float momentum;
   float dampening;
@@ -34,6 +44,7 @@ template <bool HAS_G, bool HAS_BUF>
 __global__ void __launch_bounds__(kK3Threads, 2)
 k3_dense(float* __restrict__ p, float* __restrict__ buf, const float* __restrict__ g,
          const float* __restrict__ coef_ptr, float scale, long long d, SgdHyper h) {
+  if (h.lr_ptr) h.lr = *h.lr_ptr;
   const float coef = (HAS_G && coef_ptr) ? (*coef_ptr) * scale : scale;
   const float f = h.first_step ? 1.0f : 1.0f - h.dampening;
   const float m = h.momentum;
@@ -90,7 +101,10 @@ __global__ void __launch_bounds__(256)
 k3_sparse(float* __restrict__ p, float* __restrict__ buf, const Pair* __restrict__ pairs,
           const unsigned int* __restrict__ counts, unsigned int nseg, unsigned int seg_stride,
           const float* __restrict__ coef_ptr, float scale, unsigned int d, SgdHyper h,
-          int use_atomics, unsigned int* __restrict__ bad_index_count) {
+          int use_atomics, unsigned int* __restrict__ bad_index_count,
+          const unsigned int* __restrict__ parity_word, unsigned int parity_stride) {
+  if (h.lr_ptr) h.lr = *h.lr_ptr;
+  pairs = parity_base(pairs, parity_word, parity_stride);
   const float coef = coef_ptr ? (*coef_ptr) * scale : scale;
   const float f = h.first_step ? 1.0f : 1.0f - h.dampening;
   const bool has_buf = buf != nullptr && h.momentum != 0.f;
@@ -124,7 +138,9 @@ k3_sparse(float* __restrict__ p, float* __restrict__ buf, const Pair* __restrict
 __global__ void __launch_bounds__(256)
 k3_scatter_dense(float* __restrict__ g, const Pair* __restrict__ pairs,
                  const unsigned int* __restrict__ counts, unsigned int nseg,
-                 unsigned int seg_stride, float scale, unsigned int d, int use_atomics) {
+                 unsigned int seg_stride, float scale, unsigned int d, int use_atomics,
+                 const unsigned int* __restrict__ parity_word, unsigned int parity_stride) {
+  pairs = parity_base(pairs, parity_word, parity_stride);
   const unsigned int stride = gridDim.x * blockDim.x;
   for (unsigned int s = 0; s < nseg; ++s) {
     unsigned int n = counts[s];
@@ -153,7 +169,7 @@ static int dense_grid(long long d) {
 }
 
 extern "C" int gtk_k3_dense(float* p, float* buf, const float* g, const float* coef, float scale,
-                            long long d, float lr, float momentum, float dampening,
+                            long long d, float lr, const float* lr_ptr, float momentum, float dampening,
                             float weight_decay, int nesterov, int first_step, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (d <= 0) return GTK_ERR_ARG;
@@ -164,7 +180,7 @@ extern "C" int gtk_k3_dense(float* p, float* buf, const float* g, const float* c
   if ((has_buf && (reinterpret_cast<uintptr_t>(buf) & 15u) != a) ||
       (has_g && (reinterpret_cast<uintptr_t>(g) & 15u) != a))
     return GTK_ERR_ARG;
-  SgdHyper h{lr, momentum, dampening, weight_decay, nesterov, first_step};
+  SgdHyper h{lr_ptr, lr, momentum, dampening, weight_decay, nesterov, first_step};
   const int grid = dense_grid(d);
   if (has_g && has_buf) k3_dense<true, true><<<grid, kK3Threads, 0, stream>>>(p, buf, g, coef, scale, d, h);
   else if (has_g) k3_dense<true, false><<<grid, kK3Threads, 0, stream>>>(p, p, g, coef, scale, d, h);
@@ -176,29 +192,34 @@ extern "C" int gtk_k3_dense(float* p, float* buf, const float* g, const float* c
 
 extern "C" int gtk_k3_sparse(float* p, float* buf, const void* pairs, const unsigned int* counts,
                              unsigned int nseg, unsigned int seg_stride, const float* coef,
-                             float scale, unsigned int d, float lr, float momentum, float dampening,
-                             float weight_decay, int nesterov, int first_step, int use_atomics,
-                             unsigned int* bad_index_count, void* stream_) {
+                             float scale, unsigned int d, float lr, const float* lr_ptr, float momentum,
+                             float dampening, float weight_decay, int nesterov, int first_step,
+                             int use_atomics, unsigned int* bad_index_count,
+                             const unsigned int* parity_word, unsigned int parity_stride,
+                             void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (nseg == 0 || seg_stride == 0) return GTK_ERR_ARG;
-  SgdHyper h{lr, momentum, dampening, weight_decay, nesterov, first_step};
+  SgdHyper h{lr_ptr, lr, momentum, dampening, weight_decay, nesterov, first_step};
   unsigned int blocks = (seg_stride + 255u) / 256u;
   if (blocks > 1184u) blocks = 1184u;
   k3_sparse<<<blocks, 256, 0, stream>>>(p, buf, (const Pair*)pairs, counts, nseg, seg_stride, coef,
-                                        scale, d, h, use_atomics, bad_index_count);
+                                        scale, d, h, use_atomics, bad_index_count, parity_word,
+                                        parity_stride);
   gtk_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
 }
 
 extern "C" int gtk_k3_scatter_dense(float* g, const void* pairs, const unsigned int* counts,
                                     unsigned int nseg, unsigned int seg_stride, float scale,
-                                    long long d, int use_atomics, void* stream_) {
+                                    long long d, int use_atomics, const unsigned int* parity_word,
+                                    unsigned int parity_stride, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (cudaMemsetAsync(g, 0, (size_t)d * sizeof(float), stream) != cudaSuccess) return GTK_ERR_CUDA;
   unsigned int blocks = (seg_stride + 255u) / 256u;
   if (blocks > 1184u) blocks = 1184u;
   k3_scatter_dense<<<blocks, 256, 0, stream>>>(g, (const Pair*)pairs, counts, nseg, seg_stride,
-                                               scale, (unsigned int)d, use_atomics);
+                                               scale, (unsigned int)d, use_atomics, parity_word,
+                                               parity_stride);
   gtk_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
 }

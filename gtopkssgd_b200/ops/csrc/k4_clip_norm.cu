@@ -72,7 +72,9 @@ k4_sumsq_dense(const float* __restrict__ x, long long d, ClipState* st) {
 
 __global__ void __launch_bounds__(kK4Threads)
 k4_sumsq_pairs(const Pair* __restrict__ pairs, const unsigned int* __restrict__ counts,
-               unsigned int nseg, unsigned int seg_stride, ClipState* st) {
+               unsigned int nseg, unsigned int seg_stride, ClipState* st,
+               const unsigned int* __restrict__ parity_word, unsigned int parity_stride) {
+  if (parity_word) pairs += (size_t)((*parity_word - 1u) & 1u) * parity_stride;
   double total = 0.0;
   const unsigned int stride = gridDim.x * kK4Threads;
   for (unsigned int s = 0; s < nseg; ++s) {
@@ -119,13 +121,15 @@ extern "C" int gtk_k4_sumsq_dense(const float* x, long long d, void* state, void
 }
 
 extern "C" int gtk_k4_sumsq_pairs(const void* pairs, const unsigned int* counts, unsigned int nseg,
-                                  unsigned int seg_stride, void* state, void* stream_) {
+                                  unsigned int seg_stride, void* state,
+                                  const unsigned int* parity_word, unsigned int parity_stride,
+                                  void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (nseg == 0 || seg_stride == 0) return GTK_ERR_ARG;
   unsigned int blocks = (seg_stride + kK4Threads - 1) / kK4Threads;
   if (blocks > 592u) blocks = 592u;
   k4_sumsq_pairs<<<blocks, kK4Threads, 0, stream>>>((const Pair*)pairs, counts, nseg, seg_stride,
-                                                    (ClipState*)state);
+                                                    (ClipState*)state, parity_word, parity_stride);
   gtk_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
 }

@@ -104,6 +104,9 @@ class ExchangeRank:
         self.ctrl = torch.zeros(int(L.gtk_ctrl_bytes()) // 4, dtype=torch.int32, device=dev)
         self.n_global = torch.zeros(1, dtype=torch.int32, device=dev)
         self.seg_counts = torch.zeros(MAX_PEERS, dtype=torch.int32, device=dev)
+        # call counter of this rank's exchanges: the kernel reads it at entry (flag epoch, slot parity)
+        # and adds one at exit, so launches carry no per-call argument and can be replayed from a graph
+        self.epoch = torch.ones(1, dtype=torch.int32, device=dev)
         lay = symm_layout(self.kcap, with_allgather)
         assert lay[4] <= region.nbytes, "symmetric region too small"
         self.layout = lay
@@ -113,8 +116,8 @@ class ExchangeRank:
                                            [C.c_void_p(0)] * (MAX_PEERS - world)))
         _lib.check(L.gtk_k2rank_fill(host, selector.sel.data_ptr(), selector.state.data_ptr(), self.work0.data_ptr(),
                                      self.work1.data_ptr(), self.map.data_ptr(), resid.data_ptr(), region.local_ptr,
-                                     self.ctrl.data_ptr(), self.n_global.data_ptr(), self.kcap, int(with_allgather),
-                                     world, peers), "gtk_k2rank_fill")
+                                     self.ctrl.data_ptr(), self.n_global.data_ptr(), self.epoch.data_ptr(), self.kcap,
+                                     int(with_allgather), world, peers), "gtk_k2rank_fill")
         self.desc_host = bytes(host)
         self.desc = torch.frombuffer(bytearray(self.desc_host), dtype=torch.uint8).to(dev)
 
@@ -134,6 +137,18 @@ class ExchangeRank:
         c = self.ctrl[:8].cpu()
         return int(c[_lib.CTRL_STATUS]), int(c[_lib.CTRL_WHERE])
 
+    def last_parity(self) -> int:
+        """Parity of the slot set the last completed exchange wrote (synchronises)."""
+        return (int(self.epoch.item()) - 1) & 1
+
+    @property
+    def parity_stride(self) -> int:
+        return self.kcap
+
+    @property
+    def ag_parity_stride(self) -> int:
+        return MAX_PEERS * self.kcap
+
 
 def _desc_array(ranks: Sequence[ExchangeRank]) -> torch.Tensor:
     if len(ranks) == 1:
@@ -152,7 +167,7 @@ def default_nctas(k: int, nranks: int = 1, sms: int = 148) -> int:
     return max(1, min(n, sms // max(nranks, 1)))
 
 
-def launch_gtopk(ranks: Sequence[ExchangeRank], desc: torch.Tensor, rank_base: int, world: int, k: int, epoch: int,
+def launch_gtopk(ranks: Sequence[ExchangeRank], desc: torch.Tensor, rank_base: int, world: int, k: int,
                  nctas: Optional[int] = None, limit_ms: float = 5000.0) -> None:
     """Enqueue one gTop-k exchange.  ``ranks`` are the ranks served by this
     launch (one in production, all P when emulated); ``desc`` is their
@@ -163,12 +178,12 @@ def launch_gtopk(ranks: Sequence[ExchangeRank], desc: torch.Tensor, rank_base: i
         nctas = default_nctas(k, len(ranks))
     ctrls = (C.c_void_p * len(ranks))(*[C.c_void_p(r.ctrl.data_ptr()) for r in ranks])
     code = L.gtk_k2_exchange(desc.data_ptr(), ctrls, len(ranks), rank_base, world, k, r0.kcap, r0.numel,
-                             epoch & 0xffffffff, nctas, int(limit_ms * 1e6), current_stream_handle(r0.resid.device))
+                             nctas, int(limit_ms * 1e6), current_stream_handle(r0.resid.device))
     _lib.check(code, "gtk_k2_exchange")
 
 
 def launch_allgather(ranks: Sequence[ExchangeRank], desc: torch.Tensor, seg_counts: torch.Tensor, rank_base: int,
-                     world: int, k: int, epoch: int, reselect: bool, nctas: Optional[int] = None,
+                     world: int, k: int, reselect: bool, nctas: Optional[int] = None,
                      limit_ms: float = 5000.0) -> None:
     """Enqueue one Top-k all-gather ('topk'), optionally followed by the global
     re-selection ('topk2').  ``seg_counts`` is an int32 device tensor of
@@ -179,7 +194,7 @@ def launch_allgather(ranks: Sequence[ExchangeRank], desc: torch.Tensor, seg_coun
         nctas = default_nctas(k * (world if reselect else 1) // 2 + 1, len(ranks))
     ctrls = (C.c_void_p * len(ranks))(*[C.c_void_p(r.ctrl.data_ptr()) for r in ranks])
     code = L.gtk_k2t_allgather(desc.data_ptr(), ctrls, len(ranks), rank_base, world, k, r0.kcap, r0.work_cap,
-                               r0.numel, epoch & 0xffffffff, int(reselect), seg_counts.data_ptr(), nctas,
+                               r0.numel, int(reselect), seg_counts.data_ptr(), nctas,
                                int(limit_ms * 1e6), current_stream_handle(r0.resid.device))
     _lib.check(code, "gtk_k2t_allgather")
 

@@ -52,6 +52,8 @@ def _declare(lib):
     lib.gtk_device_info.restype = vp
     lib.gtk_launch_count.restype = i64
     lib.gtk_reset_launch_count.restype = None
+    lib.gtk_count_launch.argtypes = [i32]
+    lib.gtk_count_launch.restype = None
     lib.gtk_ctrl_bytes.restype = u64
     lib.gtk_k1state_bytes.restype = u64
     lib.gtk_k2rank_bytes.restype = u64
@@ -61,21 +63,22 @@ def _declare(lib):
     lib.gtk_k1_select.restype = i32
     lib.gtk_symm_layout.argtypes = [u32, i32, C.POINTER(u64)]
     lib.gtk_symm_layout.restype = None
-    lib.gtk_k2rank_fill.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, i32, u32, C.POINTER(vp)]
+    lib.gtk_k2rank_fill.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, i32, u32, C.POINTER(vp)]
     lib.gtk_k2rank_fill.restype = i32
-    lib.gtk_k2_exchange.argtypes = [vp, C.POINTER(vp), u32, u32, u32, u32, u32, u32, u32, u32, u64, vp]
+    lib.gtk_k2_exchange.argtypes = [vp, C.POINTER(vp), u32, u32, u32, u32, u32, u32, u32, u64, vp]
     lib.gtk_k2_exchange.restype = i32
-    lib.gtk_k2t_allgather.argtypes = [vp, C.POINTER(vp), u32, u32, u32, u32, u32, u32, u32, u32, i32, vp, u32, u64, vp]
+    lib.gtk_k2t_allgather.argtypes = [vp, C.POINTER(vp), u32, u32, u32, u32, u32, u32, u32, i32, vp, u32, u64, vp]
     lib.gtk_k2t_allgather.restype = i32
-    lib.gtk_k3_dense.argtypes = [vp, vp, vp, vp, f32, i64, f32, f32, f32, f32, i32, i32, vp]
+    lib.gtk_k3_dense.argtypes = [vp, vp, vp, vp, f32, i64, f32, vp, f32, f32, f32, i32, i32, vp]
     lib.gtk_k3_dense.restype = i32
-    lib.gtk_k3_sparse.argtypes = [vp, vp, vp, vp, u32, u32, vp, f32, u32, f32, f32, f32, f32, i32, i32, i32, vp, vp]
+    lib.gtk_k3_sparse.argtypes = [vp, vp, vp, vp, u32, u32, vp, f32, u32, f32, vp, f32, f32, f32, i32, i32, i32, vp,
+                                  vp, u32, vp]
     lib.gtk_k3_sparse.restype = i32
-    lib.gtk_k3_scatter_dense.argtypes = [vp, vp, vp, u32, u32, f32, i64, i32, vp]
+    lib.gtk_k3_scatter_dense.argtypes = [vp, vp, vp, u32, u32, f32, i64, i32, vp, u32, vp]
     lib.gtk_k3_scatter_dense.restype = i32
     lib.gtk_k4_sumsq_dense.argtypes = [vp, i64, vp, vp]
     lib.gtk_k4_sumsq_dense.restype = i32
-    lib.gtk_k4_sumsq_pairs.argtypes = [vp, vp, u32, u32, vp, vp]
+    lib.gtk_k4_sumsq_pairs.argtypes = [vp, vp, u32, u32, vp, vp, u32, vp]
     lib.gtk_k4_sumsq_pairs.restype = i32
     lib.gtk_k4_finalize.argtypes = [vp, f32, f32, vp, vp]
     lib.gtk_k4_finalize.restype = i32
@@ -137,3 +140,9 @@ def launch_count() -> int:
 
 def reset_launch_count() -> None:
     lib().gtk_reset_launch_count()
+
+
+def add_launches(n: int) -> None:
+    """Account for kernels of this library that a replayed CUDA graph launched."""
+    if n:
+        lib().gtk_count_launch(int(n))

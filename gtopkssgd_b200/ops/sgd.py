@@ -30,7 +30,8 @@ class SgdHyper:
 
 
 def sgd_dense(p: torch.Tensor, buf: Optional[torch.Tensor], h: SgdHyper, first_step: bool,
-              g: Optional[torch.Tensor] = None, scale: float = 1.0, coef: Optional[torch.Tensor] = None) -> None:
+              g: Optional[torch.Tensor] = None, scale: float = 1.0, coef: Optional[torch.Tensor] = None,
+              lr_dev: Optional[torch.Tensor] = None) -> None:
     """Dense part of the step over a flat parameter buffer.  With ``g`` given
     (dense mode) the gradient is ``coef * scale * g``."""
     d = p.numel()
@@ -43,7 +44,7 @@ def sgd_dense(p: torch.Tensor, buf: Optional[torch.Tensor], h: SgdHyper, first_s
         return
     L = _lib.lib()
     code = L.gtk_k3_dense(p.data_ptr(), _ptr(buf), _ptr(g), _ptr(coef), C.c_float(scale), d, C.c_float(h.lr),
-                          C.c_float(h.momentum), C.c_float(h.dampening), C.c_float(h.weight_decay),
+                          _ptr(lr_dev), C.c_float(h.momentum), C.c_float(h.dampening), C.c_float(h.weight_decay),
                           int(h.nesterov), int(first_step), current_stream_handle(p.device))
     _lib.check(code, "gtk_k3_dense")
 
@@ -51,12 +52,17 @@ def sgd_dense(p: torch.Tensor, buf: Optional[torch.Tensor], h: SgdHyper, first_s
 def sgd_sparse(p: torch.Tensor, buf: Optional[torch.Tensor], pairs: torch.Tensor, counts: torch.Tensor,
                nseg: int, seg_stride: int, h: SgdHyper, first_step: bool, scale: float,
                coef: Optional[torch.Tensor] = None, use_atomics: bool = False,
-               bad_index_count: Optional[torch.Tensor] = None) -> None:
+               bad_index_count: Optional[torch.Tensor] = None, lr_dev: Optional[torch.Tensor] = None,
+               parity_word: Optional[torch.Tensor] = None, parity_stride: int = 0) -> None:
     """Sparse part of the step: for every pair (j, v) of every segment add
     ``coef * scale * v`` as gradient of element j.  ``counts`` is a device
-    tensor with the live length of each segment."""
+    tensor with the live length of each segment.  ``lr_dev`` (a device scalar)
+    overrides ``h.lr``; ``parity_word`` selects the half of a two-parity buffer
+    on the device: base = pairs + ((word - 1) & 1) * parity_stride."""
     d = p.numel()
     if p.device.type != "cuda":
+        if parity_word is not None:
+            pairs = pairs[((int(parity_word) - 1) & 1) * parity_stride:]
         c = scale * (float(coef) if coef is not None else 1.0)
         f = 1.0 if first_step else 1.0 - h.dampening
         for s in range(nseg):
@@ -74,17 +80,21 @@ def sgd_sparse(p: torch.Tensor, buf: Optional[torch.Tensor], pairs: torch.Tensor
     if bad_index_count is None:
         bad_index_count = _scratch_word(p.device)
     code = L.gtk_k3_sparse(p.data_ptr(), _ptr(buf), pairs.data_ptr(), counts.data_ptr(), nseg, seg_stride,
-                           _ptr(coef), C.c_float(scale), d, C.c_float(h.lr), C.c_float(h.momentum),
+                           _ptr(coef), C.c_float(scale), d, C.c_float(h.lr), _ptr(lr_dev), C.c_float(h.momentum),
                            C.c_float(h.dampening), C.c_float(h.weight_decay), int(h.nesterov), int(first_step),
-                           int(use_atomics), bad_index_count.data_ptr(), current_stream_handle(p.device))
+                           int(use_atomics), bad_index_count.data_ptr(), _ptr(parity_word), int(parity_stride),
+                           current_stream_handle(p.device))
     _lib.check(code, "gtk_k3_sparse")
 
 
 def scatter_dense(g: torch.Tensor, pairs: torch.Tensor, counts: torch.Tensor, nseg: int, seg_stride: int,
-                  scale: float, use_atomics: bool = False) -> None:
+                  scale: float, use_atomics: bool = False, parity_word: Optional[torch.Tensor] = None,
+                  parity_stride: int = 0) -> None:
     """g <- 0, then g[j] (+)= scale * v for every pair: the dense averaged
     gradient, for callers that want to inspect ``p.grad``."""
     if g.device.type != "cuda":
+        if parity_word is not None:
+            pairs = pairs[((int(parity_word) - 1) & 1) * parity_stride:]
         g.zero_()
         for s in range(nseg):
             n = int(counts[s])
@@ -93,7 +103,8 @@ def scatter_dense(g: torch.Tensor, pairs: torch.Tensor, counts: torch.Tensor, ns
         return
     L = _lib.lib()
     code = L.gtk_k3_scatter_dense(g.data_ptr(), pairs.data_ptr(), counts.data_ptr(), nseg, seg_stride,
-                                  C.c_float(scale), g.numel(), int(use_atomics), current_stream_handle(g.device))
+                                  C.c_float(scale), g.numel(), int(use_atomics), _ptr(parity_word), int(parity_stride),
+                                  current_stream_handle(g.device))
     _lib.check(code, "gtk_k3_scatter_dense")
 
 

@@ -63,6 +63,17 @@ class SparseResult:
     seg_stride: int
     use_atomics: bool
     scale: float
+    # two-parity buffers of the exchange kernel: the live half is chosen on the device from the
+    # exchange's call counter, base = pairs + ((word - 1) & 1) * parity_stride (None: single buffer)
+    parity_word: Optional[torch.Tensor] = None
+    parity_stride: int = 0
+
+    def live_pairs(self) -> torch.Tensor:
+        """The live half as a tensor (reads the counter: synchronises)."""
+        if self.parity_word is None:
+            return self.pairs
+        off = ((int(self.parity_word.item()) - 1) & 1) * self.parity_stride
+        return self.pairs[off:off + self.nseg * self.seg_stride]
 
 
 class GroupEngine:
@@ -74,7 +85,7 @@ class GroupEngine:
         self.grad = fb.group_slice(fb.grad, g)
         self.resid = fb.group_slice(fb.residual, g) if fb.residual is not None else None
         self.numel = g.numel
-        self.epoch = 0
+        self.last_k = 0
         self.result: Optional[SparseResult] = None
         self.dense_ready = False
         dev = fb.device
@@ -93,9 +104,9 @@ class GroupEngine:
             self.region = ex.SymmetricRegion.create_ipc(nbytes, group=comm.cpu_group())
             self.rank_ctx = ex.ExchangeRank(owner.rank(), world, self.numel, self.max_k, self.selector, self.resid,
                                             self.region, with_allgather=with_ag, reselect=(mode == "topk2"))
-            self.gout = [ex.pairs_view(self.rank_ctx.gout_ptr(p), self.max_k, dev) for p in (0, 1)]
+            self.gout = ex.pairs_view(self.rank_ctx.gout_ptr(0), 2 * self.max_k, dev)
             if with_ag:
-                self.ag = [ex.pairs_view(self.rank_ctx.ag_ptr(p), ex.MAX_PEERS * self.max_k, dev) for p in (0, 1)]
+                self.ag = ex.pairs_view(self.rank_ctx.ag_ptr(0), 2 * ex.MAX_PEERS * self.max_k, dev)
         elif world > 1:
             cap = self.max_k * (world if mode == "topk" else 1)
             self.host_pairs = torch.zeros((cap, 2), dtype=torch.int32, device=dev)
@@ -108,30 +119,32 @@ class GroupEngine:
         world, mode = o.size(), o.mode
         k = oracle.num_selected(self.numel, density)
         k = min(k, self.max_k)
-        self.epoch += 1
+        self.last_k = k
         t = o.timers
-        t.timer(self.g.key, "compression").start()
+        t.start(self.g.key, "compression")
         self.selector.select(self.grad, self.resid, k, g_scale=g_scale)
-        t.timer(self.g.key, "compression").stop()
-        t.timer(self.g.key, "allreduce").start()
+        t.stop(self.g.key, "compression")
+        t.start(self.g.key, "allreduce")
         if world == 1:
             self.result = SparseResult(self.selector.sel, self.selector.n_sel_tensor, 1, self.max_k, False, 1.0)
         elif self.is_cuda:
-            parity = self.epoch & 1
             rc = self.rank_ctx
             if mode == "gtopk":
-                ex.launch_gtopk([rc], rc.desc, o.rank(), world, k, self.epoch, limit_ms=o.wait_limit_ms)
-                self.result = SparseResult(self.gout[parity], rc.n_global, 1, self.max_k, False, 1.0 / world)
+                ex.launch_gtopk([rc], rc.desc, o.rank(), world, k, limit_ms=o.wait_limit_ms)
+                self.result = SparseResult(self.gout, rc.n_global, 1, self.max_k, False, 1.0 / world,
+                                           rc.epoch, rc.parity_stride)
             else:
-                ex.launch_allgather([rc], rc.desc, rc.seg_counts, o.rank(), world, k, self.epoch,
+                ex.launch_allgather([rc], rc.desc, rc.seg_counts, o.rank(), world, k,
                                     reselect=(mode == "topk2"), limit_ms=o.wait_limit_ms)
                 if mode == "topk":
-                    self.result = SparseResult(self.ag[parity], rc.seg_counts, world, self.max_k, True, 1.0 / world)
+                    self.result = SparseResult(self.ag, rc.seg_counts, world, self.max_k, True, 1.0 / world,
+                                               rc.epoch, rc.ag_parity_stride)
                 else:
-                    self.result = SparseResult(self.gout[parity], rc.n_global, 1, self.max_k, False, 1.0 / world)
+                    self.result = SparseResult(self.gout, rc.n_global, 1, self.max_k, False, 1.0 / world,
+                                               rc.epoch, rc.parity_stride)
         else:
             self._reduce_host(k, world, mode)
-        t.timer(self.g.key, "allreduce").stop()
+        t.stop(self.g.key, "allreduce")
 
     def _reduce_host(self, k: int, world: int, mode: str) -> None:
         """CPU tensors: the gloo fallback (also the multi-process oracle)."""
@@ -261,11 +274,11 @@ class AllReducer:
         eng = self.engines[gi]
         key = eng.g.key
         if self.mode == "none":
-            self.timers.timer(key, "allreduce").start()
+            self.timers.start(key, "allreduce")
             if self.size() > 1:
                 fallback.dense_allreduce(eng.grad)
             eng.dense_ready = True
-            self.timers.timer(key, "allreduce").stop()
+            self.timers.stop(key, "allreduce")
             self.allreduce_count += 1
             return
         if settings.PROFILING_NORM:
@@ -330,9 +343,10 @@ class AllReducer:
         with torch.no_grad():
             res = eng.result
             sparse = torch.zeros_like(dense_ref)
+            live = res.live_pairs()
             for s in range(res.nseg):
                 n = int(res.counts[s])
-                idx, val = pairs_to_tensors(res.pairs[s * res.seg_stride:(s + 1) * res.seg_stride], n)
+                idx, val = pairs_to_tensors(live[s * res.seg_stride:(s + 1) * res.seg_stride], n)
                 sparse.index_add_(0, idx.to(sparse.device), val.to(sparse.device) * res.scale)
             k = oracle.num_selected(eng.numel, self.get_current_density())
             perm = torch.randperm(dense_ref.numel(), device=dense_ref.device)[:k]

@@ -75,6 +75,11 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         self._arrived = [0] * len(self._flat.groups)
         self._launched = [False] * len(self._flat.groups)
         self._expected = [len(g.names) for g in self._flat.groups]
+        # learning rate as the kernels see it: a device scalar, refreshed whenever the host value
+        # changes, so that a captured CUDA graph follows the LR schedule
+        self._lr_dev = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._lr_host = None
+        self.capturing = False
         self._post_clip: Optional[ClipNorm] = None
         self._post_coef: Optional[torch.Tensor] = None
         self._hook_handles = []
@@ -145,7 +150,8 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         if materialize and not self._materialized and self._allreducer.mode != "none":
             for eng in self._allreducer.engines:
                 r = eng.result
-                scatter_dense(eng.grad, r.pairs, r.counts, r.nseg, r.seg_stride, r.scale, r.use_atomics)
+                scatter_dense(eng.grad, r.pairs, r.counts, r.nseg, r.seg_stride, r.scale, r.use_atomics,
+                              r.parity_word, r.parity_stride)
             self._materialized = True
 
     def clip_grad_norm(self, max_norm: float) -> torch.Tensor:
@@ -170,10 +176,18 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             scale = 1.0
             for eng in a.engines:
                 r = eng.result
-                self._post_clip.add_pairs(r.pairs, r.counts, r.nseg, r.seg_stride)
+                self._post_clip.add_pairs(r.pairs, r.counts, r.nseg, r.seg_stride, r.parity_word, r.parity_stride)
                 scale = r.scale
             self._post_coef = self._post_clip.finalize(max_norm, scale=scale)
         return self._post_coef
+
+    def sync_lr(self) -> None:
+        """Copy the host learning rate to the device scalar if it changed
+        (never called while a graph is being captured)."""
+        lr = float(self.param_groups[0]["lr"])
+        if lr != self._lr_host and not self.capturing:
+            self._lr_dev.fill_(lr)
+            self._lr_host = lr
 
     def _hyper(self) -> SgdHyper:
         g = self.param_groups[0]
@@ -187,7 +201,9 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         it is enqueued before the compute stream waits for the side stream: it
         runs while the exchange kernel is still waiting on its peers."""
         loss = closure() if closure is not None else None
+        self.sync_lr()
         h = self._hyper()
+        lr_dev = self._lr_dev
         first = self._step_count == 0
         fb, a = self._flat, self._allreducer
         use_buf = h.momentum != 0 and not self.momentum_correction
@@ -201,23 +217,24 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             # accumulation micro-step: plain local SGD on the raw gradient
             for eng in a.engines:
                 p, buf = bufs(eng)
-                sgd_dense(p, buf, h, first, g=eng.grad, scale=1.0)
+                sgd_dense(p, buf, h, first, g=eng.grad, scale=1.0, lr_dev=lr_dev)
         elif a.mode == "none" or self._materialized:
             self.synchronize()
             scale = 1.0 / a.size() if a.mode == "none" else 1.0
             for eng in a.engines:
                 p, buf = bufs(eng)
-                sgd_dense(p, buf, h, first, g=eng.grad, scale=scale, coef=self._post_coef)
+                sgd_dense(p, buf, h, first, g=eng.grad, scale=scale, coef=self._post_coef, lr_dev=lr_dev)
         else:
             for eng in a.engines:
                 p, buf = bufs(eng)
-                sgd_dense(p, buf, h, first)
+                sgd_dense(p, buf, h, first, lr_dev=lr_dev)
             self.synchronize()
             for eng in a.engines:
                 p, buf = bufs(eng)
                 r = eng.result
                 sgd_sparse(p, buf, r.pairs, r.counts, r.nseg, r.seg_stride, h, first, r.scale, coef=self._post_coef,
-                           use_atomics=r.use_atomics)
+                           use_atomics=r.use_atomics, lr_dev=lr_dev, parity_word=r.parity_word,
+                           parity_stride=r.parity_stride)
         if use_buf and first:
             for name, slot in fb.slots.items():
                 self.state[slot.param]["momentum_buffer"] = fb.momentum_view(name)

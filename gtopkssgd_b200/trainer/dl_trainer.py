@@ -62,7 +62,7 @@ class DLTrainer:
     def __init__(self, rank, size, master="gpu10", dist=True, ngpus=1, batch_size=32, is_weak_scaling=True,
                  data_dir="./data", dataset="cifar10", dnn="resnet20", lr=0.04, nworkers=1, prefix=None,
                  sparsity=0.95, pretrain=None, num_steps=35, tb_writer=None, device=None, save_checkpoints=None,
-                 synthetic_train_size=None):
+                 synthetic_train_size=None, cuda_graph=None):
         self.size, self.rank = size, rank
         self.pretrain, self.dataset, self.prefix = pretrain, dataset, prefix
         self.num_steps, self.ngpus, self.writer = num_steps, ngpus, tb_writer
@@ -77,6 +77,8 @@ class DLTrainer:
                                  if save_checkpoints is None else bool(save_checkpoints))
         self.train_sampler = None
         self.ext = None
+        self.use_cuda_graph = os.environ.get("GTOPK_CUDA_GRAPH", "0") == "1" if cuda_graph is None else bool(cuda_graph)
+        self._graphed = None
         if not isinstance(dnn, str):
             self.net, self.dnn = dnn, dnn.name
         else:
@@ -554,6 +556,44 @@ class DLTrainer:
         if self.dnn == "lstm":
             return num_of_iters, hidden
         return num_of_iters
+
+    def train_step(self, data=None, hidden=None, clip_norm=None, cuda_graph=None):
+        """One complete iteration: zero_grad, forward, backward, optional
+        gradient-norm clip, optimizer step.  With ``cuda_graph`` (default: the
+        trainer's ``use_cuda_graph``) the whole iteration is captured once as a
+        CUDA graph and replayed.  Returns the carried hidden state for the LSTM
+        model, else None."""
+        use_graph = self.use_cuda_graph if cuda_graph is None else cuda_graph
+        if not (use_graph and self.is_cuda and self.dnn != "lstman4"):
+            self.optimizer.zero_grad()
+            if self.dnn == "lstm":
+                _, hidden = self.train(1, data=data, hidden=hidden)
+            else:
+                self.train(1, data=data)
+            if clip_norm is not None:
+                if hasattr(self.optimizer, "clip_grad_norm"):
+                    self.optimizer.clip_grad_norm(clip_norm)
+                else:
+                    torch.nn.utils.clip_grad_norm_(self.net.parameters(), clip_norm)
+            self.update_model()
+            return hidden
+        from .graphed_step import GraphedStep
+        if self._graphed is None or self._graphed.clip_norm != clip_norm:
+            self._graphed = GraphedStep(self, clip_norm=clip_norm)
+        s = time.time()
+        self.adjust_learning_rate(self.train_epoch, self.optimizer)
+        if self.train_iter % self.num_batches_per_epoch == 0 and self.train_iter > 0:
+            self._epoch_boundary()
+        batch = self.data_iter() if data is None else data
+        x, y, _, _ = self._to_device(batch)
+        loss, acc, hidden = self._graphed.run(x, y, hidden)
+        self._loss_t = loss
+        self._avg_loss_t = loss.clone() if self._avg_loss_t is None else self._avg_loss_t + loss
+        if acc is not None:
+            self.train_acc_top1.append(acc.clone())
+        self.train_iter += 1
+        self.timer += time.time() - s
+        return hidden
 
     def test(self, epoch):
         """Validation: accuracy (CNNs), perplexity (LSTM LM), WER (AN4)."""

@@ -75,6 +75,14 @@ class PhaseTimers:
             d[phase] = CudaTimer(self.enabled)
         return d[phase]
 
+    def start(self, group: str, phase: str) -> None:
+        if self.enabled:
+            self.timer(group, phase).start()
+
+    def stop(self, group: str, phase: str) -> None:
+        if self.enabled:
+            self.timer(group, phase).stop()
+
     def add_host(self, group: str, phase: str, seconds: float) -> None:
         if self.enabled:
             self._host[group][phase].append(seconds)

@@ -61,6 +61,49 @@ def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="
     return trace
 
 
+def graphed_step_worker(rank, world, iters, compressor):
+    """Whole-iteration CUDA graph (3 eager warm-up iterations, then replays)
+    with a learning rate that changes between replays."""
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+    from gtopkssgd_b200.trainer.dl_trainer import DLTrainer
+    from gtopkssgd_b200.trainer.graphed_step import GraphedStep
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("WARNING")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    comm.init(backend="nccl")
+    torch.manual_seed(0)
+    t = DLTrainer(rank, world, dist=False, ngpus=1, batch_size=8, data_dir="synthetic", dataset="cifar10",
+                  dnn="resnet20", lr=0.1, nworkers=world, device=dev, synthetic_train_size=256)
+    comm.broadcast_parameters(t.net.state_dict(), 0)
+    dopt = DistributedOptimizer(t.optimizer, t.net.named_parameters(), compression=compressors[compressor],
+                                is_sparse=compressor != "none", density=0.001, wait_limit_ms=20000)
+    t.update_optimizer(dopt)
+    fb = dopt._flat
+    step = GraphedStep(t, warmup=3)
+    trace = {"p0": fb.param.detach().cpu().clone(), "grads": [], "params": [], "resid": [], "lrs": [],
+             "numel": fb.numel}
+    for it in range(iters):
+        x, y = _make_batch(rank, it, 8)
+        lr = 0.1 if it < 4 else 0.05
+        for pg in dopt.param_groups:
+            pg["lr"] = lr
+        step.run(x.to(dev), y.to(dev))
+        torch.cuda.synchronize()
+        trace["lrs"].append(lr)
+        trace["grads"].append(fb.grad.detach().cpu().clone())
+        trace["params"].append(fb.param.detach().cpu().clone())
+        trace["resid"].append(fb.residual.detach().cpu().clone())
+    dopt.check_status()
+    trace["graphs"] = len(step.graphs)
+    dopt.stop()
+    comm.shutdown()
+    return trace
+
+
 def failing_peer_worker(rank, world, mode):
     """Fault injection on the host: rank 1 leaves (or stalls) before the
     exchange; rank 0 must get a PeerTimeout / err_handler call, not a hang."""

@@ -43,7 +43,8 @@ def replay_and_check(traces, density, compressor, rtol=1e-5, atol=1e-6):
             assert all(torch.equal(grads[0], g) for g in grads[1:])
             dense = grads[0] / world
         for r in range(world):
-            oracle.sgd_step(params[r], bufs[r], dense, 0.1, 0.9, 0.0, 1e-4, False, first_step=(it == 0))
+            lr = traces[r]["lrs"][it] if "lrs" in traces[r] else 0.1
+            oracle.sgd_step(params[r], bufs[r], dense, lr, 0.9, 0.0, 1e-4, False, first_step=(it == 0))
             got = traces[r]["params"][it][:numel]
             assert torch.allclose(got, params[r], rtol=rtol, atol=atol), (it, r, float((got - params[r]).abs().max()))
             if compressor != "none":

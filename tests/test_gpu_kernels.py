@@ -240,14 +240,14 @@ def test_k2_gtopk_exchange_emulated(P, d, k, nctas):
         grads = [torch.randn(d, device=DEV) for _ in range(P)]
         for r, g in zip(ranks, grads):
             r.selector.select(g, r.resid, k)
-        ex.launch_gtopk(ranks, desc, 0, P, k, epoch, nctas=nctas, limit_ms=2000)
+        ex.launch_gtopk(ranks, desc, 0, P, k, nctas=nctas, limit_ms=2000)
         torch.cuda.synchronize()
         for r in ranks:
             assert r.status() == (0, 0)
         glob, _ = oracle.simulate_gtopk_step([g.cpu() for g in grads], res_ref, k)
         ref = dict(zip(glob[0].tolist(), glob[1].tolist()))
         for r in ranks:
-            gi, gv = _read_gout(r, epoch & 1)
+            gi, gv = _read_gout(r, r.last_parity())
             got = dict(zip(gi.cpu().tolist(), gv.cpu().tolist()))
             assert len(got) == gi.numel()
             assert set(got) == set(ref), "rank %d" % r.rank
@@ -270,7 +270,7 @@ def test_k2t_allgather_emulated(P, mode):
         grads = [torch.randn(d, device=DEV) for _ in range(P)]
         for r, g in zip(ranks, grads):
             r.selector.select(g, r.resid, k)
-        ex.launch_allgather(ranks, desc, seg_counts, 0, P, k, epoch, reselect=(mode == "topk2"), nctas=2,
+        ex.launch_allgather(ranks, desc, seg_counts, 0, P, k, reselect=(mode == "topk2"), nctas=2,
                             limit_ms=2000)
         torch.cuda.synchronize()
         local = [oracle.compress(g.cpu(), rr, k) for g, rr in zip(grads, res_ref)]
@@ -278,7 +278,8 @@ def test_k2t_allgather_emulated(P, mode):
             assert r.status() == (0, 0)
             counts = seg_counts[r.rank * ex.MAX_PEERS:r.rank * ex.MAX_PEERS + P].cpu().tolist()
             assert counts == [k] * P
-            base = r.layout[1] + (epoch & 1) * ex.MAX_PEERS * k * 8
+            assert r.last_parity() == epoch & 1
+            base = r.layout[1] + r.last_parity() * ex.MAX_PEERS * k * 8
             for q in range(P):
                 raw = r.region._owner[base + q * k * 8: base + (q + 1) * k * 8].view(torch.int32).view(k, 2)
                 qi, qv = pairs_to_tensors(raw, k)
@@ -289,7 +290,7 @@ def test_k2t_allgather_emulated(P, mode):
             for rr, loc in zip(res_ref, local):
                 oracle.put_back(rr, loc, gi_ref)
             for r in ranks:
-                gi, gv = _read_gout(r, epoch & 1)
+                gi, gv = _read_gout(r, r.last_parity())
                 got = dict(zip(gi.cpu().tolist(), gv.cpu().tolist()))
                 assert set(got) == set(ref)
                 for j in ref:
@@ -306,14 +307,16 @@ def test_k2_bounded_wait_reports_timeout():
     ranks, desc = _emulated_world(2, d, k)
     g = torch.randn(d, device=DEV)
     ranks[0].selector.select(g, ranks[0].resid, k)
-    ex.launch_gtopk(ranks[:1], ranks[0].desc, 0, 2, k, 1, nctas=2, limit_ms=50)
+    ex.launch_gtopk(ranks[:1], ranks[0].desc, 0, 2, k, nctas=2, limit_ms=50)
     torch.cuda.synchronize()
     status, where = ranks[0].status()
     assert status == 1 and 210 <= where < 220
     # the device is still healthy and the next (complete) exchange works
     for r in ranks:
         r.selector.select(torch.randn(d, device=DEV), r.resid, k)
-    ex.launch_gtopk(ranks, desc, 0, 2, k, 2, nctas=1, limit_ms=2000)
+    assert int(ranks[0].epoch.item()) == 1  # the aborted call did not advance the counter
+    ex.launch_gtopk(ranks, desc, 0, 2, k, nctas=1, limit_ms=2000)
     torch.cuda.synchronize()
     assert all(r.status() == (0, 0) for r in ranks)
+    assert [int(r.epoch.item()) for r in ranks] == [2, 2]
     assert int(ranks[1].n_global.item()) == k

@@ -45,6 +45,20 @@ def test_eight_gpu_gtopk_matches_oracle():
     replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
 
 
+def test_single_gpu_cuda_graph_step_matches_oracle():
+    traces = spawn_ranks(_workers.graphed_step_worker, 1, args=(7, "gtopk"), timeout_s=600)
+    assert traces[0]["graphs"] == 1
+    replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("compressor", ["gtopk", "none"])
+def test_two_gpu_cuda_graph_step_matches_oracle(compressor):
+    traces = spawn_ranks(_workers.graphed_step_worker, 2, args=(7, compressor), timeout_s=600,
+                         env={"NCCL_NVLS_ENABLE": "0"})
+    replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
+
+
 def test_graft_smoke():
     import __graft_entry__ as g
     g.smoke()
