@@ -174,7 +174,7 @@ def main():
 
     e2e = None
     if not args.skip_e2e:
-        for _ in range(max(2, args.warmup // 2)):
+        for _ in range(max(6, args.warmup)):  # covers the eager warm-up and the graph capture of this arm
             e2e_step()
         e2e_dev_s, e2e_wall = timed(e2e_step, args.steps)
         e2e = {"value": bs * world * args.steps / e2e_dev_s, "unit": "samples/s", "h2d_bytes_per_step": h2d_bytes,

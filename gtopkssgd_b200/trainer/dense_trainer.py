@@ -29,7 +29,7 @@ writer = None
 
 
 def ssgd_dense(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, nwpernode, pretrain,
-               num_steps=1, max_iters=None, threshold=None):
+               num_steps=1, max_iters=None, threshold=None, cuda_graph=None):
     use_cuda = torch.cuda.is_available()
     rank = comm.rank()
     if use_cuda:
@@ -39,7 +39,7 @@ def ssgd_dense(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, 
     trainer = DLTrainer(rank, nworkers, dist=False, batch_size=batch_size, is_weak_scaling=True,
                         ngpus=1 if use_cuda else 0, data_dir=data_dir, dataset=dataset, dnn=dnn, lr=lr,
                         nworkers=nworkers, prefix="allreduce", pretrain=pretrain, num_steps=num_steps,
-                        tb_writer=writer)
+                        tb_writer=writer, cuda_graph=cuda_graph)
     trainer.set_train_epoch(int(comm.broadcast_object(trainer.get_train_epoch())))
     trainer.set_train_iter(int(comm.broadcast_object(trainer.get_train_iter())))
     comm.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
@@ -54,18 +54,20 @@ def ssgd_dense(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, 
             hidden = trainer.net.init_hidden() if dnn == "lstm" else None
             for i in range(iters_per_epoch):
                 s = time.time()
-                optimizer.zero_grad()
-                for j in range(nsteps_update):
-                    optimizer.local = j < nsteps_update - 1 and nsteps_update > 1
-                    if dnn == "lstm":
-                        _, hidden = trainer.train(1, hidden=hidden)
-                    else:
-                        trainer.train(1)
-                if dnn == "lstm":
-                    optimizer.clip_grad_norm(0.25)
-                elif dnn == "lstman4":
-                    optimizer.clip_grad_norm(400)
-                trainer.update_model()
+                clip = 0.25 if dnn == "lstm" else 400 if dnn == "lstman4" else None
+                if nsteps_update == 1:
+                    hidden = trainer.train_step(hidden=hidden, clip_norm=clip)
+                else:
+                    optimizer.zero_grad()
+                    for j in range(nsteps_update):
+                        optimizer.local = j < nsteps_update - 1
+                        if dnn == "lstm":
+                            _, hidden = trainer.train(1, hidden=hidden)
+                        else:
+                            trainer.train(1)
+                    if clip is not None:
+                        optimizer.clip_grad_norm(clip)
+                    trainer.update_model()
                 if i % display == 0 and use_cuda:
                     torch.cuda.synchronize()
                 times.append(time.time() - s)
@@ -102,6 +104,7 @@ def main(argv=None):
     p.add_argument("--num-steps", type=int, default=35)
     p.add_argument("--max-iters", type=int, default=None)
     p.add_argument("--threshold", type=int, default=None)
+    p.add_argument("--cuda-graph", action="store_true")
     args = p.parse_args(argv)
     comm.init()
     if comm.size() > 1:
@@ -121,7 +124,8 @@ def main(argv=None):
     logger.info("Configurations: %s", args)
     try:
         ssgd_dense(args.dnn, args.dataset, args.data_dir, args.nworkers, args.lr, args.batch_size, args.nsteps_update,
-                   args.max_epochs, args.nwpernode, args.pretrain, args.num_steps, args.max_iters, args.threshold)
+                   args.max_epochs, args.nwpernode, args.pretrain, args.num_steps, args.max_iters, args.threshold,
+                   args.cuda_graph or None)
     finally:
         if writer is not None:
             writer.close()

@@ -50,6 +50,10 @@ class GraphedStep:
         acc = None
         if t.dnn not in ("lstm", "lstman4"):
             acc = t.cal_accuracy(outputs.detach(), y, topk=(1,))[0]
+        # nothing returned may keep the autograd graph alive: gradient accumulators that survive an
+        # iteration remember the stream they were created on, which breaks a later capture
+        if hidden is not None:
+            hidden = repackage_hidden(hidden)
         return loss.detach(), acc, hidden
 
     def _signature(self, x, y) -> Tuple:

@@ -51,7 +51,7 @@ def _dump_profiling_norms(optimizer, rank, epoch):
 
 def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, compression=False,
                 compressor="topk", nwpernode=1, sigma_scale=2.5, pretrain=None, density=0.01, prefix=None,
-                max_iters=None, threshold=None, save_checkpoints=None, check_every=50):
+                max_iters=None, threshold=None, save_checkpoints=None, check_every=50, cuda_graph=None):
     use_cuda = torch.cuda.is_available()
     rank = dopt.rank()
     if use_cuda:
@@ -62,7 +62,7 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
     trainer = DLTrainer(rank, nworkers, dist=False, batch_size=batch_size, is_weak_scaling=True,
                         ngpus=1 if use_cuda else 0, data_dir=data_dir, dataset=dataset, dnn=dnn, lr=lr,
                         nworkers=nworkers, prefix=prefix, pretrain=pretrain, tb_writer=writer,
-                        save_checkpoints=save_checkpoints)
+                        save_checkpoints=save_checkpoints, cuda_graph=cuda_graph)
     trainer.set_train_epoch(comm.broadcast_object(trainer.get_train_epoch()))
     trainer.set_train_iter(comm.broadcast_object(trainer.get_train_iter()))
 
@@ -88,18 +88,20 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
             hidden = trainer.net.init_hidden() if dnn == "lstm" else None
             for i in range(iters_per_epoch):
                 s = time.time()
-                optimizer.zero_grad()
-                for j in range(nsteps_update):
-                    optimizer.local = j < nsteps_update - 1 and nsteps_update > 1
-                    if dnn == "lstm":
-                        _, hidden = trainer.train(1, hidden=hidden)
-                    else:
-                        trainer.train(1)
-                if dnn == "lstm":
-                    optimizer.clip_grad_norm(0.25)
-                elif dnn == "lstman4":
-                    optimizer.clip_grad_norm(400)
-                trainer.update_model()
+                clip = 0.25 if dnn == "lstm" else 400 if dnn == "lstman4" else None
+                if nsteps_update == 1:
+                    hidden = trainer.train_step(hidden=hidden, clip_norm=clip)
+                else:
+                    optimizer.zero_grad()
+                    for j in range(nsteps_update):
+                        optimizer.local = j < nsteps_update - 1
+                        if dnn == "lstm":
+                            _, hidden = trainer.train(1, hidden=hidden)
+                        else:
+                            trainer.train(1)
+                    if clip is not None:
+                        optimizer.clip_grad_norm(clip)
+                    trainer.update_model()
                 if i % display == 0 or (check_every and done % check_every == 0):
                     if use_cuda:
                         torch.cuda.synchronize()
@@ -146,6 +148,8 @@ def build_parser():
     p.add_argument("--threshold", type=int, default=None, help="Merge threshold in elements")
     p.add_argument("--pin-density", action="store_true", help="Use --density from epoch 0 on")
     p.add_argument("--save-checkpoints", action="store_true", help="Write a checkpoint at every epoch end")
+    p.add_argument("--cuda-graph", action="store_true",
+                   help="Capture the whole iteration as a CUDA graph (pays off for launch-bound models)")
     p.set_defaults(compression=False)
     return p
 
@@ -182,7 +186,8 @@ def main(argv=None):
         robust_ssgd(args.dnn, args.dataset, args.data_dir, args.nworkers, args.lr, args.batch_size,
                     args.nsteps_update, args.max_epochs, args.compression, args.compressor, args.nwpernode,
                     args.sigma_scale, args.pretrain, args.density, prefix, max_iters=args.max_iters,
-                    threshold=args.threshold, save_checkpoints=args.save_checkpoints or None)
+                    threshold=args.threshold, save_checkpoints=args.save_checkpoints or None,
+                    cuda_graph=args.cuda_graph or None)
     finally:
         if writer is not None:
             writer.close()
