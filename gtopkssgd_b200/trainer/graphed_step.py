@@ -97,10 +97,17 @@ class GraphedStep:
         self.graphs[sig], self.static[sig] = g, st
         return g, st
 
+    def capturable(self) -> bool:
+        """Dense multi-GPU training keeps NCCL collectives inside the iteration;
+        capturing those needs the process group's asynchronous error handling
+        switched off before it is created, so that case stays eager."""
+        a = getattr(self.t.optimizer, "_allreducer", None)
+        return not (a is not None and a.mode == "none" and a.size() > 1)
+
     def run(self, x, y, hidden=None):
         """x, y: this iteration's batch on the device.  Returns (loss, acc, hidden)."""
         t, opt = self.t, self.t.optimizer
-        if self.eager_done < self.warmup:
+        if self.eager_done < self.warmup or not self.capturable():
             self.eager_done += 1
             if hidden is not None:
                 hidden = repackage_hidden(hidden)

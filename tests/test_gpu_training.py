@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("compressor", ["gtopk", "none"])
 def test_single_gpu_training_matches_oracle(compressor):
-    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 1, args=(4, 0.001, compressor, "cuda"), timeout_s=600)
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 1, args=(4, 0.001, compressor, "cuda"), timeout_s=300)
     replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
 
 
@@ -22,7 +22,7 @@ def test_single_gpu_training_matches_oracle(compressor):
 @pytest.mark.parametrize("compressor", ["gtopk", "topk", "topk2", "none"])
 def test_two_gpu_training_matches_oracle(compressor):
     env = {"NCCL_NVLS_ENABLE": "0"}
-    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 2, args=(4, 0.001, compressor, "cuda"), timeout_s=600,
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 2, args=(4, 0.001, compressor, "cuda"), timeout_s=300,
                          env=env)
     replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
 
@@ -31,7 +31,7 @@ def test_two_gpu_training_matches_oracle(compressor):
 def test_four_gpu_gtopk_matches_oracle():
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
-    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 4, args=(3, 0.001, "gtopk", "cuda"), timeout_s=600,
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 4, args=(3, 0.001, "gtopk", "cuda"), timeout_s=300,
                          env={"NCCL_NVLS_ENABLE": "0"})
     replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
 
@@ -40,22 +40,25 @@ def test_four_gpu_gtopk_matches_oracle():
 def test_eight_gpu_gtopk_matches_oracle():
     if torch.cuda.device_count() < 8:
         pytest.skip("needs 8 GPUs")
-    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 8, args=(3, 0.001, "gtopk", "cuda"), timeout_s=600,
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 8, args=(3, 0.001, "gtopk", "cuda"), timeout_s=300,
                          env={"NCCL_NVLS_ENABLE": "0"})
     replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
 
 
 def test_single_gpu_cuda_graph_step_matches_oracle():
-    traces = spawn_ranks(_workers.graphed_step_worker, 1, args=(7, "gtopk"), timeout_s=600)
+    traces = spawn_ranks(_workers.graphed_step_worker, 1, args=(7, "gtopk"), timeout_s=300)
     assert traces[0]["graphs"] == 1
     replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
 
 
 @pytest.mark.multigpu
-@pytest.mark.parametrize("compressor", ["gtopk", "none"])
-def test_two_gpu_cuda_graph_step_matches_oracle(compressor):
-    traces = spawn_ranks(_workers.graphed_step_worker, 2, args=(7, compressor), timeout_s=600,
+@pytest.mark.parametrize("compressor,graphs", [("gtopk", 1), ("none", 0)])
+def test_two_gpu_cuda_graph_step_matches_oracle(compressor, graphs):
+    """gTop-k iterations are captured (peer-store exchange inside the graph);
+    dense multi-GPU iterations stay eager by design."""
+    traces = spawn_ranks(_workers.graphed_step_worker, 2, args=(7, compressor), timeout_s=240,
                          env={"NCCL_NVLS_ENABLE": "0"})
+    assert traces[0]["graphs"] == graphs
     replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
 
 
