@@ -123,9 +123,11 @@ struct RankBarrier {
   unsigned int nctas;
   unsigned int gen;
   uint64_t limit_ns;
+  unsigned int* counter = nullptr;  // arrival counter; nullptr: ctrl->bar
 
   __device__ __forceinline__ bool sync(uint32_t where) {
     __shared__ int ok_s;
+    unsigned int* const arrivals = counter ? counter : &ctrl->bar;
     if (nctas == 1) {
       __syncthreads();
       return !aborted(ctrl);
@@ -135,11 +137,11 @@ struct RankBarrier {
     if (threadIdx.x == 0) {
       int ok = 1;
       __threadfence();
-      red_release_gpu_add(&ctrl->bar, 1u);
+      red_release_gpu_add(arrivals, 1u);
       const unsigned int target = gen * nctas;
       const uint64_t t0 = globaltimer_ns();
       unsigned int spins = 0;
-      while (ld_acquire_gpu_u32(&ctrl->bar) < target) {
+      while (ld_acquire_gpu_u32(arrivals) < target) {
         if (aborted(ctrl)) { ok = 0; break; }
         if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > limit_ns) {
           record_error(ctrl, ST_TIMEOUT_BARRIER, where);

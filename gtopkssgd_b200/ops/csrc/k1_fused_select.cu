@@ -1,33 +1,47 @@
-// K1: fused residual add + magnitude top-k selection + residual write-back.
+// K1: fused residual add + magnitude top-k selection + residual write-back,
+// one cooperative kernel.
 //
 // Replaces the op sequence of the reference's TopKCompressor.compress
 // (compression.py:32-57: add_, abs, topk, gather, mask fill/scatter, mul, sub_)
 // and the gather of the selected values (allreducer.py:543).
 //
-// Two launches:
-//   k1_stream  one streaming pass over g and r (read 8d bytes, write 4d bytes):
-//              acc = g*scale + r; entries with |acc| >= tau become candidates
-//              (appended to a bounded list, r <- 0), all others r <- acc.
-//              tau is a device-resident prediction from the previous call.
-//   k1_finish  cooperative kernel.  Normal mode: exact radix select of the k
-//              largest magnitudes among the C candidates (k <= C <= cap),
-//              rejected candidates go back into r, tau is re-predicted from the
-//              measured tail slope.  Exact mode (C < k or the list overflowed;
-//              always on the first call, when tau is +inf): restore r = acc from
-//              the stored candidates, then a 3-pass radix select over all d
-//              entries of r and one collect pass.
+// Phase 1 (all CTAs)  one streaming pass over g and r (read 8d bytes, write 4d):
+//     acc = g*scale + r; entries with |acc| >= tau become candidates (appended to
+//     a bounded list, r <- 0, first radix digit counted), all others r <- acc.
+//     tau is a device-resident prediction from the previous call.
+// grid barrier
+// Phase 2  normal mode (k <= C <= cap candidates): the first C/1024 CTAs run the
+//     remaining two radix passes over the candidates, compact the k winners,
+//     return the rejected candidates to r and re-predict tau from the measured
+//     tail slope; the other CTAs leave.
+//     exact mode (C < k or the list overflowed; always on the first call, when
+//     tau is +inf): all CTAs restore r = acc from the stored candidates, then run
+//     a 3-pass radix select over all d entries of r and one collect pass.
 // The dense sparsified gradient of the reference is never materialised; the
 // output is k (int32 index, fp32 value) pairs in no particular order.
+//
+// No host-side clearing: the caller provides two control blocks; call i uses
+// block (i & 1) and zeroes the other one for call i + 1 (i is K1State::n_calls,
+// read on the device, so the launch can be replayed from a CUDA graph).
 #include <cstddef>
 #include "select_common.cuh"
 #include "host_api.h"
 
 namespace gtk {
 
-constexpr int kK1Threads = 512;
+constexpr int kK1Threads = kSelThreads;    // 512
 constexpr int kK1Vec = 4;                  // float4 loads of g and of r in flight per thread
 constexpr int kWarpStage = 128;            // pairs staged per warp
 constexpr int kWarpFlushAt = kWarpStage - 32;
+
+struct StreamShared {
+  Pair wstage[kK1Threads / 32][kWarpStage];  // per-warp candidate staging
+  unsigned int hist[kHistBins];              // first radix digit of this CTA's candidates
+};
+constexpr size_t kK1SmemBytes =
+    sizeof(StreamShared) > sizeof(SelectShared) ? sizeof(StreamShared) : sizeof(SelectShared);
+// bytes of a control block that K1 dirties: header, trace, two histogram sets
+constexpr size_t kK1ClearBytes = offsetof(Ctrl, hist) + 2 * sizeof(((Ctrl*)0)->hist[0]);
 
 __device__ __forceinline__ void warp_flush(Pair* wbuf, unsigned int& wcnt, Pair* cand,
                                            unsigned int cap, unsigned int* counter, float* r) {
@@ -47,18 +61,14 @@ __device__ __forceinline__ void warp_flush(Pair* wbuf, unsigned int& wcnt, Pair*
   __syncwarp();
 }
 
-__global__ void __launch_bounds__(kK1Threads, 2)
-k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __restrict__ g_scale,
-          const K1State* __restrict__ st, Pair* __restrict__ cand, unsigned int cap, Ctrl* ctrl,
-          long long d) {
-  __shared__ Pair wstage[kK1Threads / 32][kWarpStage];
-  __shared__ unsigned int shist[kHistBins];  // first radix digit of every candidate of this CTA
-  for (int i = threadIdx.x; i < kHistBins; i += kK1Threads) shist[i] = 0u;
+__device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __restrict__ g,
+                                             float* __restrict__ r, float scale, float tau,
+                                             Pair* __restrict__ cand, unsigned int cap, Ctrl* ctrl,
+                                             long long d) {
+  for (int i = threadIdx.x; i < kHistBins; i += kK1Threads) ss.hist[i] = 0u;
   __syncthreads();
-  Pair* wbuf = wstage[threadIdx.x >> 5];
+  Pair* wbuf = ss.wstage[threadIdx.x >> 5];
   unsigned int wcnt = 0;
-  const float tau = st->tau;
-  const float scale = g_scale ? *g_scale : 1.0f;
   unsigned int* counter = &ctrl->n_out;
 
   // Leading scalars up to the first 16-byte boundary (g and r share the offset).
@@ -117,7 +127,7 @@ k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __res
               p.idx = (int32_t)(head + (v << 2) + e);
               p.val = a[e];
               wbuf[wcnt + __popc(m & lanemask_lt())] = p;
-              atomicAdd(&shist[mag_key(a[e]) >> 20], 1u);
+              atomicAdd(&ss.hist[mag_key(a[e]) >> 20], 1u);
             }
             wcnt += __popc(m);
             if (wcnt > (unsigned int)kWarpFlushAt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
@@ -147,7 +157,7 @@ k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __res
           p.idx = (int32_t)i;
           p.val = a;
           wbuf[wcnt + __popc(m & lanemask_lt())] = p;
-          atomicAdd(&shist[mag_key(a) >> 20], 1u);
+          atomicAdd(&ss.hist[mag_key(a) >> 20], 1u);
         }
         wcnt += __popc(m);
         if (wcnt > (unsigned int)kWarpFlushAt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
@@ -155,10 +165,10 @@ k1_stream(const float* __restrict__ g, float* __restrict__ r, const float* __res
     }
   }
   if (wcnt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
-  // publish this CTA's part of the first-pass histogram (k1_finish starts from it)
+  // publish this CTA's part of the first-pass histogram
   __syncthreads();
   for (int i = threadIdx.x; i < kHistBins; i += kK1Threads) {
-    const unsigned int c = shist[i];
+    const unsigned int c = ss.hist[i];
     if (c) atomicAdd(&ctrl->hist[0][0][i], c);
   }
 }
@@ -178,12 +188,32 @@ __device__ __forceinline__ float predict_tau(float t_k, float tau_used, unsigned
   return next > 0.f ? next : 0.f;
 }
 
-__global__ void __launch_bounds__(kSelThreads)
-k1_finish(float* __restrict__ r, long long d, Pair* __restrict__ cand, unsigned int cap,
-          Pair* __restrict__ sel, unsigned int k, K1State* st, Ctrl* ctrl, float target_ratio,
-          unsigned long long limit_ns) {
-  __shared__ SelectShared s;
-  const unsigned int count = ctrl->n_out;
+__global__ void __launch_bounds__(kK1Threads, 2)
+k1_fused(const float* __restrict__ g, float* __restrict__ r, const float* __restrict__ g_scale,
+         long long d, Pair* __restrict__ cand, unsigned int cap, Pair* __restrict__ sel,
+         unsigned int k, K1State* st, Ctrl* ctrl_pair, float target_ratio,
+         unsigned long long limit_ns) {
+  __shared__ __align__(16) unsigned char smem_raw[kK1SmemBytes];
+  // Every CTA reads the call parity before the grid barrier; it is advanced after it.
+  const unsigned int calls = st->n_calls;
+  Ctrl* ctrl = ctrl_pair + (calls & 1u);
+  {  // prepare the other control block for the next call
+    uint4* other = reinterpret_cast<uint4*>(ctrl_pair + ((calls & 1u) ^ 1u));
+    const size_t nvec16 = kK1ClearBytes / 16;
+    for (size_t i = (size_t)blockIdx.x * kK1Threads + threadIdx.x; i < nvec16;
+         i += (size_t)gridDim.x * kK1Threads)
+      other[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  const float tau_used = st->tau;
+  const float scale = g_scale ? *g_scale : 1.0f;
+  stream_phase(*reinterpret_cast<StreamShared*>(smem_raw), g, r, scale, tau_used, cand, cap, ctrl, d);
+
+  RankBarrier bar_all{ctrl, gridDim.x, 0u, limit_ns};
+  if (!bar_all.sync(90)) return;
+  if (blockIdx.x == 0 && threadIdx.x == 0) st->n_calls = calls + 1u;
+
+  SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
+  const unsigned int count = __ldcg(&ctrl->n_out);
   const unsigned int C = count < cap ? count : cap;
   const bool exact_mode = (count > cap) || (C < k);
   Threshold th;
@@ -194,8 +224,8 @@ k1_finish(float* __restrict__ r, long long d, Pair* __restrict__ cand, unsigned 
     if (nct < 1u) nct = 1u;
     if (nct > gridDim.x) nct = gridDim.x;
     if (blockIdx.x >= nct) return;
-    RankBarrier bar{ctrl, nct, 0u, limit_ns};
-    auto key_at = [&](unsigned int i) -> uint32_t { return mag_key(cand[i].val); };
+    RankBarrier bar{ctrl, nct, 0u, limit_ns, &ctrl->scratch[0]};
+    auto key_at = [&](unsigned int i) -> uint32_t { return mag_key(ld_pair_cg(&cand[i]).val); };
     if (!radix_select_kth(s, bar, blockIdx.x, nct, C, k, ctrl->hist[0], key_at, &th, 100, true))
       return;
     StagedAppender app{&s, sel, &ctrl->cursor[0], k, ctrl};
@@ -205,7 +235,7 @@ k1_finish(float* __restrict__ r, long long d, Pair* __restrict__ cand, unsigned 
     for (unsigned int t = 0; t < trips; ++t) {
       const unsigned int i = t * stride + blockIdx.x * kSelThreads + threadIdx.x;
       if (i < C) {
-        const Pair e = cand[i];
+        const Pair e = ld_pair_cg(&cand[i]);
         if (passes_threshold(mag_key(e.val), th, &ctrl->tie[0])) {
           app.put(e);
         } else {
@@ -217,11 +247,9 @@ k1_finish(float* __restrict__ r, long long d, Pair* __restrict__ cand, unsigned 
     app.flush(none);
     if (blockIdx.x == 0 && threadIdx.x == 0) {
       const float t_k = __uint_as_float(th.key);
-      const float tau_used = st->tau;
       st->n_sel = k;
       st->n_cand = count;
       st->fallback = 0u;
-      st->n_calls += 1u;
       st->kth_mag = t_k;
       st->tau = predict_tau(t_k, tau_used, C, k, target_ratio);
     }
@@ -230,16 +258,15 @@ k1_finish(float* __restrict__ r, long long d, Pair* __restrict__ cand, unsigned 
 
   // Exact mode: every CTA of the grid takes part.
   const unsigned int nct = gridDim.x;
-  RankBarrier bar{ctrl, nct, 0u, limit_ns};
   const unsigned int stride = nct * kSelThreads;
   for (unsigned int i = blockIdx.x * kSelThreads + threadIdx.x; i < C; i += stride) {
-    const Pair e = cand[i];
+    const Pair e = ld_pair_cg(&cand[i]);
     r[e.idx] = e.val;
   }
-  if (!bar.sync(110)) return;
+  if (!bar_all.sync(110)) return;
   const unsigned int n = (unsigned int)d;
   auto key_at = [&](unsigned int i) -> uint32_t { return mag_key(__ldcg(&r[i])); };
-  if (!radix_select_kth(s, bar, blockIdx.x, nct, n, k, ctrl->hist[1], key_at, &th, 120)) return;
+  if (!radix_select_kth(s, bar_all, blockIdx.x, nct, n, k, ctrl->hist[1], key_at, &th, 120)) return;
   StagedAppender app{&s, sel, &ctrl->cursor[1], k, ctrl};
   app.begin();
   const unsigned int trips = (n + stride - 1) / stride;
@@ -264,7 +291,6 @@ k1_finish(float* __restrict__ r, long long d, Pair* __restrict__ cand, unsigned 
     st->n_cand = count;
     st->fallback = 1u;
     st->n_fallbacks += 1u;
-    st->n_calls += 1u;
     st->kth_mag = t_k;
     st->tau = predict_tau(t_k, 0.f, 0u, k, target_ratio);
   }
@@ -276,55 +302,58 @@ using namespace gtk;
 
 extern "C" unsigned long long gtk_ctrl_bytes(void) { return sizeof(Ctrl); }
 
+namespace {
+// Co-resident CTAs of k1_fused on the current device (cached).
+int k1_max_grid() {
+  static int cached = 0;
+  if (cached) return cached;
+  const DeviceInfo* di = gtk_device_info();
+  if (!di) return 0;
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k1_fused, kK1Threads, 0) != cudaSuccess ||
+      occ < 1)
+    return 0;
+  if (occ > 2) occ = 2;
+  cached = di->sms * occ;
+  return cached;
+}
+
+int k1_launch(const float* g, float* r, const float* g_scale, long long d, unsigned int k,
+              Pair* cand, unsigned int cap, Pair* sel, K1State* st, Ctrl* ctrl_pair,
+              float target_ratio, unsigned long long limit_ns, cudaStream_t stream) {
+  const int max_grid = k1_max_grid();
+  if (max_grid < 1) return GTK_ERR_CUDA;
+  const long long tile = (long long)kK1Threads * kK1Vec;
+  const long long ntiles = ((d / 4) + tile - 1) / tile;
+  long long want = (cap + 1023u) / 1024u;  // CTAs the candidate select can use
+  if (ntiles > want) want = ntiles;
+  int grid = want < max_grid ? (int)(want > 0 ? want : 1) : max_grid;
+  void* args[] = {&g, &r, &g_scale, &d, &cand, &cap, &sel, &k, &st, &ctrl_pair, &target_ratio, &limit_ns};
+  const cudaError_t e = cudaLaunchCooperativeKernel((void*)k1_fused, dim3(grid), dim3(kK1Threads),
+                                                    args, 0, stream);
+  gtk_count_launch(1);
+  return e == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
+}
+}  // namespace
+
+// ctrl: TWO consecutive control blocks (2 * gtk_ctrl_bytes()), zero when first used.
 extern "C" int gtk_k1_select(const float* g, float* r, const float* g_scale, long long d,
                              unsigned int k, void* cand, unsigned int cap, void* sel, void* state,
                              void* ctrl, float target_ratio, unsigned long long limit_ns,
                              void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
   if (d <= 0 || d >= (1ll << 31) || k == 0 || k > cap) return GTK_ERR_ARG;
   // g and r must share their offset inside a 16-byte line (same flat layout)
   if ((reinterpret_cast<uintptr_t>(g) & 15u) != (reinterpret_cast<uintptr_t>(r) & 15u) ||
       (reinterpret_cast<uintptr_t>(r) & 3u) != 0u)
     return GTK_ERR_ARG;
-  const DeviceInfo* di = gtk_device_info();
-  if (!di) return GTK_ERR_CUDA;
-  // header + trace + the two histogram sets K1 can touch
-  const size_t clear_bytes = offsetof(Ctrl, hist) + 2 * sizeof(((Ctrl*)0)->hist[0]);
-  cudaError_t e = cudaMemsetAsync(ctrl, 0, clear_bytes, stream);
-  if (e != cudaSuccess) return GTK_ERR_CUDA;
-  const long long nvec = d / 4;
-  const long long tile = (long long)kK1Threads * kK1Vec;
-  long long ntiles = (nvec + tile - 1) / tile;
-  int grid = di->sms * 2;
-  if (ntiles < grid) grid = ntiles > 0 ? (int)ntiles : 1;
-  k1_stream<<<grid, kK1Threads, 0, stream>>>(g, r, g_scale, (const K1State*)state, (Pair*)cand, cap,
-                                             (Ctrl*)ctrl, d);
-  gtk_count_launch(1);
-  static int finish_grid = 0;
-  if (!finish_grid) {
-    int occ = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k1_finish, kSelThreads, 0);
-    if (occ < 1) return GTK_ERR_CUDA;
-    if (occ > 2) occ = 2;
-    finish_grid = di->sms * occ;
-  }
-  float* r_ = r;
-  Pair* cand_ = (Pair*)cand;
-  Pair* sel_ = (Pair*)sel;
-  K1State* st_ = (K1State*)state;
-  Ctrl* ctrl_ = (Ctrl*)ctrl;
-  void* args[] = {&r_, &d, &cand_, &cap, &sel_, &k, &st_, &ctrl_, &target_ratio, &limit_ns};
-  e = cudaLaunchCooperativeKernel((void*)k1_finish, dim3(finish_grid), dim3(kSelThreads), args, 0,
-                                  stream);
-  gtk_count_launch(1);
-  if (e != cudaSuccess) return GTK_ERR_CUDA;
-  return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
+  return k1_launch(g, r, g_scale, d, k, (Pair*)cand, cap, (Pair*)sel, (K1State*)state, (Ctrl*)ctrl,
+                   target_ratio, limit_ns, (cudaStream_t)stream_);
 }
 
 // ---------------------------------------------------------------------------
 // Allocation-free variant (declared and documented in k1_select_noalloc.h).
 // The scratch that gtk_k1_select takes from its caller lives here in a static
-// device array; the kernels are the ones above, unchanged.
+// device array; the kernel is the one above, unchanged.
 // ---------------------------------------------------------------------------
 #include <mutex>
 #include "k1_select_noalloc.h"
@@ -333,24 +362,24 @@ namespace {
 
 constexpr unsigned int kNoAllocMaxK = 16384u;
 constexpr unsigned int kNoAllocCap = 131072u;                         // candidate pairs (8 x max k)
-constexpr size_t kNoAllocCtrlOff = 0;
-constexpr size_t kNoAllocStateOff = (sizeof(Ctrl) + 255) / 256 * 256;
+constexpr size_t kNoAllocCtrlOff = 0;                                  // two control blocks
+constexpr size_t kNoAllocStateOff = (2 * sizeof(Ctrl) + 255) / 256 * 256;
 constexpr size_t kNoAllocCandOff = kNoAllocStateOff + 256;
 constexpr size_t kNoAllocBytes = kNoAllocCandOff + (size_t)kNoAllocCap * sizeof(Pair);
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never an address.
+// Static device storage starts zeroed, which is what the control blocks need on first use.
 static __device__ __align__(256) unsigned char g_k1_noalloc_scratch[kNoAllocBytes];
 
+// Forget the predicted threshold.  The call counter is left alone: it decides which
+// control block is clean.
 __global__ void k1_noalloc_reset_state(K1State* st) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     st->tau = __int_as_float(0x7f800000);  // +inf: the next call takes the exact path
     st->n_sel = 0u;
     st->n_cand = 0u;
     st->fallback = 0u;
-    st->n_fallbacks = 0u;
-    st->n_calls = 0u;
     st->kth_mag = 0.f;
-    st->reserved = 0u;
   }
 }
 
@@ -360,7 +389,6 @@ __global__ void k1_noalloc_publish_count(const K1State* st, unsigned int* n_sel_
 
 struct NoAllocDevice {
   unsigned char* base = nullptr;  // device address of g_k1_noalloc_scratch on this device
-  int finish_grid = 0;
 };
 std::mutex g_noalloc_mu;
 NoAllocDevice g_noalloc_dev[64];
@@ -390,41 +418,23 @@ extern "C" int gtk_k1_select_noalloc(const float* g, float* r, long long d, unsi
       // once per device, with that device current
       void* p = nullptr;
       if (cudaGetSymbolAddress(&p, g_k1_noalloc_scratch) != cudaSuccess || !p) return GTK_ERR_CUDA;
-      int occ = 0;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k1_finish, kSelThreads, 0) !=
-              cudaSuccess || occ < 1)
-        return GTK_ERR_CUDA;
-      slot.finish_grid = di->sms * (occ > 2 ? 2 : occ);
       slot.base = static_cast<unsigned char*>(p);
       first = true;
     }
     dev = slot;
   }
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(dev.base + kNoAllocCtrlOff);
+  Ctrl* ctrl_pair = reinterpret_cast<Ctrl*>(dev.base + kNoAllocCtrlOff);
   K1State* st = reinterpret_cast<K1State*>(dev.base + kNoAllocStateOff);
   Pair* cand = reinterpret_cast<Pair*>(dev.base + kNoAllocCandOff);
-  unsigned int cap = kNoAllocCap;
   if (first || reset_threshold) {
     k1_noalloc_reset_state<<<1, 32, 0, stream>>>(st);
     gtk_count_launch(1);
   }
-  // the control block must start at zero; everything else in the scratch is overwritten before use
-  if (cudaMemsetAsync(ctrl, 0, sizeof(Ctrl), stream) != cudaSuccess) return GTK_ERR_CUDA;
-  const long long nvec = d / 4;
-  const long long tile = (long long)kK1Threads * kK1Vec;
-  const long long ntiles = (nvec + tile - 1) / tile;
-  int grid = di->sms * 2;
-  if (ntiles < grid) grid = ntiles > 0 ? (int)ntiles : 1;
-  k1_stream<<<grid, kK1Threads, 0, stream>>>(g, r, nullptr, st, cand, cap, ctrl, d);
-  gtk_count_launch(1);
-  Pair* sel = static_cast<Pair*>(sel_out);
-  float target_ratio = 3.0f;
-  unsigned long long limit_ns = 2000000000ull;
-  void* args[] = {&r, &d, &cand, &cap, &sel, &k, &st, &ctrl, &target_ratio, &limit_ns};
-  if (cudaLaunchCooperativeKernel((void*)k1_finish, dim3(dev.finish_grid), dim3(kSelThreads), args,
-                                  0, stream) != cudaSuccess)
-    return GTK_ERR_CUDA;
-  gtk_count_launch(1);
+  // What must start at zero -- the control block of this call -- was cleared by the previous call
+  // (or is still in its initial zero state); the candidate list is overwritten before it is read.
+  const int code = k1_launch(g, r, nullptr, d, k, cand, kNoAllocCap, static_cast<Pair*>(sel_out), st,
+                             ctrl_pair, 3.0f, 2000000000ull, stream);
+  if (code != GTK_OK) return code;
   if (n_sel_out) {
     k1_noalloc_publish_count<<<1, 32, 0, stream>>>(st, n_sel_out);
     gtk_count_launch(1);

@@ -17,7 +17,7 @@
 //     acc = g + r;  sel_out <- the k largest-magnitude (int32 idx, fp32 acc) pairs;
 //     r <- acc off the selection, 0 on it;  g is not modified.
 // The scratch memory (control block, threshold-prediction state, candidate
-// list; about 1.2 MB) lives in a file-scope static __device__ array inside the
+// list; about 1.3 MB) lives in a file-scope static __device__ array inside the
 // library, so every GPU that loads the library holds that array until the
 // process exits.  The caller passes only inputs and outputs.  No call to
 // cudaMalloc, cudaFree or any allocating library routine is made.
@@ -29,10 +29,11 @@
 //  * All calls on one device share the one scratch array.  Two calls that overlap
 //    on the GPU (different streams without ordering, or several host threads)
 //    race on it: order them on one stream or with events.
-//  * The array keeps the previous call's contents: the control block is cleared
-//    at the start of every call; the predicted threshold is deliberately kept
-//    (it only steers speed, never the result) and is forgotten when
-//    reset_threshold != 0.
+//  * The array keeps the previous call's contents.  What has to start at zero is
+//    the control block of a call: the array holds two of them, every call clears
+//    the one the next call will use, and static device storage starts zeroed.
+//    The predicted threshold is deliberately kept (it only steers speed, never
+//    the result) and is forgotten when reset_threshold != 0.
 //  * The first call on each device resolves the device address of the scratch
 //    array (cudaGetSymbolAddress) and initialises the threshold state.  Make that
 //    first call before any stream capture begins.

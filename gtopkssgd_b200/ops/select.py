@@ -50,7 +50,9 @@ class TopkSelector:
             L = _lib.lib()
             assert L.gtk_k1state_bytes() == 32
             self.cand = torch.empty((self.cap, 2), dtype=torch.int32, device=self.device)
-            self.ctrl = torch.zeros(int(L.gtk_ctrl_bytes()) // 4, dtype=torch.int32, device=self.device)
+            # two control blocks: call i uses block i & 1 and clears the other one for call i + 1
+            self.ctrl_words = int(L.gtk_ctrl_bytes()) // 4
+            self.ctrl = torch.zeros(2 * self.ctrl_words, dtype=torch.int32, device=self.device)
         self.last_k = 0
 
     # -- state ---------------------------------------------------------------
@@ -71,10 +73,22 @@ class TopkSelector:
                 "n_fallbacks": int(s[4]), "n_calls": int(s[5]), "kth_mag": float(f[6])}
 
     def status(self) -> Tuple[int, int]:
+        """(status, code location) of the last failure in either control block,
+        (0, 0) if none.  Synchronises."""
         if not self.is_cuda:
             return (0, 0)
-        c = self.ctrl[:8].cpu()
-        return int(c[_lib.CTRL_STATUS]), int(c[_lib.CTRL_WHERE])
+        for b in (0, 1):
+            c = self.ctrl[b * self.ctrl_words:b * self.ctrl_words + 8].cpu()
+            if int(c[_lib.CTRL_STATUS]):
+                return int(c[_lib.CTRL_STATUS]), int(c[_lib.CTRL_WHERE])
+        return (0, 0)
+
+    def reset(self) -> None:
+        """Back to the initial state (after a reported failure)."""
+        if self.is_cuda:
+            self.ctrl.zero_()
+        self.state.zero_()
+        self.reset_threshold()
 
     # -- the op ----------------------------------------------------------------
     def select(self, g: torch.Tensor, r: torch.Tensor, k: int, g_scale: Optional[torch.Tensor] = None) -> None:

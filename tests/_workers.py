@@ -92,8 +92,6 @@ def graphed_step_worker(rank, world, iters, compressor):
         for pg in dopt.param_groups:
             pg["lr"] = lr
         step.run(x.to(dev), y.to(dev))
-        if compressor == "none":
-            dopt.synchronize()
         torch.cuda.synchronize()
         trace["lrs"].append(lr)
         trace["grads"].append(fb.grad.detach().cpu().clone())
