@@ -15,7 +15,7 @@ def _make_batch(rank, it, bs):
     return torch.randn(bs, 3, 32, 32, generator=g), torch.randint(0, 10, (bs,), generator=g)
 
 
-def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="cpu"):
+def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="cpu", threshold=None):
     """BASELINE config: ResNet-20, batch 32 per worker would be slow on CPU;
     batch 8 keeps the same code path.  Returns the final flat parameters."""
     from gtopkssgd_b200 import settings
@@ -38,10 +38,11 @@ def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="
     opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
     sparse = compressor != "none"
     dopt = DistributedOptimizer(opt, net.named_parameters(), compression=compressors[compressor], is_sparse=sparse,
-                                density=density, wait_limit_ms=20000)
+                                density=density, wait_limit_ms=20000, threshold=threshold)
     crit = torch.nn.CrossEntropyLoss()
     fb = dopt._flat
-    trace = {"p0": fb.param.detach().cpu().clone(), "grads": [], "params": [], "resid": []}
+    trace = {"p0": fb.param.detach().cpu().clone(), "grads": [], "params": [], "resid": [],
+             "groups": [(g.start, g.numel) for g in fb.groups]}
     for it in range(iters):
         x, y = _make_batch(rank, it, 8)
         dopt.zero_grad()

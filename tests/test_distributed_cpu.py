@@ -14,41 +14,48 @@ import _workers
 def replay_and_check(traces, density, compressor, rtol=1e-5, atol=1e-6):
     """Teacher-forced replay: every iteration the oracle gets the gradients the
     workers actually produced and must reproduce their parameters and
-    residuals.  (Comparing free-running trajectories instead would be
-    chaotic: one flipped top-k entry changes every later gradient.)"""
+    residuals, merged group by merged group.  (Comparing free-running
+    trajectories instead would be chaotic: one flipped top-k entry changes every
+    later gradient.)"""
     world = len(traces)
-    numel = traces[0]["numel"]
     total = traces[0]["p0"].numel()
-    k = oracle.num_selected(numel, density)
-    res = [torch.zeros(numel) for _ in range(world)]
-    bufs = [torch.zeros(numel) for _ in range(world)]
-    params = [t["p0"][:numel].clone() for t in traces]
-    assert total - numel < 64  # one group: only tail padding
+    groups = traces[0].get("groups") or [(0, traces[0]["numel"])]
+    res = [torch.zeros(total) for _ in range(world)]
+    bufs = [torch.zeros(total) for _ in range(world)]
+    params = [t["p0"].clone() for t in traces]
     for it in range(len(traces[0]["grads"])):
-        grads = [t["grads"][it][:numel] for t in traces]
-        if compressor == "gtopk":
-            glob, _ = oracle.simulate_gtopk_step(grads, res, k)
-            dense = oracle.scatter_average(glob, numel, world)
-        elif compressor == "topk":
-            local = [oracle.compress(g, r, k) for g, r in zip(grads, res)]
-            dense = oracle.topk_allgather_sum(local, numel) / world
-        elif compressor == "topk2":
-            local = [oracle.compress(g, r, k) for g, r in zip(grads, res)]
-            gi, gv = oracle.topk2_reselect(local, k)
-            for r, loc in zip(res, local):
-                oracle.put_back(r, loc, gi)
-            dense = oracle.scatter_average((gi, gv), numel, world)
-        else:
-            # dense mode reduces in place inside the hook: the recorded buffer already holds the sum
-            assert all(torch.equal(grads[0], g) for g in grads[1:])
-            dense = grads[0] / world
+        dense = torch.zeros(total)
+        for start, numel in groups:
+            sl = slice(start, start + numel)
+            k = oracle.num_selected(numel, density)
+            grads = [t["grads"][it][sl] for t in traces]
+            rs = [r[sl] for r in res]  # views: updated in place
+            if compressor == "gtopk":
+                glob, _ = oracle.simulate_gtopk_step(grads, rs, k)
+                dense[sl] = oracle.scatter_average(glob, numel, world)
+            elif compressor == "topk":
+                local = [oracle.compress(g, r, k) for g, r in zip(grads, rs)]
+                dense[sl] = oracle.topk_allgather_sum(local, numel) / world
+            elif compressor == "topk2":
+                local = [oracle.compress(g, r, k) for g, r in zip(grads, rs)]
+                gi, gv = oracle.topk2_reselect(local, k)
+                for r, loc in zip(rs, local):
+                    oracle.put_back(r, loc, gi)
+                dense[sl] = oracle.scatter_average((gi, gv), numel, world)
+            else:
+                # dense mode reduces in place inside the hook: the recorded buffer already holds the sum
+                assert all(torch.equal(grads[0], g) for g in grads[1:])
+                dense[sl] = grads[0] / world
         for r in range(world):
             lr = traces[r]["lrs"][it] if "lrs" in traces[r] else 0.1
             oracle.sgd_step(params[r], bufs[r], dense, lr, 0.9, 0.0, 1e-4, False, first_step=(it == 0))
-            got = traces[r]["params"][it][:numel]
-            assert torch.allclose(got, params[r], rtol=rtol, atol=atol), (it, r, float((got - params[r]).abs().max()))
-            if compressor != "none":
-                assert torch.allclose(traces[r]["resid"][it][:numel], res[r], rtol=rtol, atol=atol), (it, r)
+            got = traces[r]["params"][it]
+            for start, numel in groups:  # padding between groups is not compared
+                sl = slice(start, start + numel)
+                assert torch.allclose(got[sl], params[r][sl], rtol=rtol, atol=atol), \
+                    (it, r, start, float((got[sl] - params[r][sl]).abs().max()))
+                if compressor != "none":
+                    assert torch.allclose(traces[r]["resid"][it][sl], res[r][sl], rtol=rtol, atol=atol), (it, r, start)
             params[r] = got.clone()  # teacher forcing
     for r in range(1, world):  # replicas stay identical
         assert torch.equal(traces[0]["params"][-1], traces[r]["params"][-1])
@@ -58,6 +65,14 @@ def replay_and_check(traces, density, compressor, rtol=1e-5, atol=1e-6):
 def test_resnet20_two_workers_gloo_matches_oracle(compressor):
     traces = spawn_ranks(_workers.resnet20_gtopk_worker, 2, args=(3, 0.001, compressor), timeout_s=600)
     replay_and_check(traces, 0.001, compressor)
+
+
+def test_two_workers_three_merge_groups_gloo():
+    """Merge threshold of 100 000 elements: ResNet-20 splits into three groups,
+    each selected and exchanged on its own."""
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 2, args=(3, 0.001, "gtopk", "cpu", 100000), timeout_s=600)
+    assert len(traces[0]["groups"]) == 3
+    replay_and_check(traces, 0.001, "gtopk")
 
 
 def test_four_workers_gtopk_gloo():

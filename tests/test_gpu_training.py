@@ -18,6 +18,21 @@ def test_single_gpu_training_matches_oracle(compressor):
     replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
 
 
+def test_single_gpu_three_merge_groups_overlap_backward():
+    """Three merged groups: the select of a finished group runs on the side
+    stream while backward continues."""
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 1, args=(4, 0.001, "gtopk", "cuda", 100000), timeout_s=300)
+    assert len(traces[0]["groups"]) == 3
+    replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.multigpu
+def test_two_gpu_three_merge_groups():
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 2, args=(4, 0.001, "gtopk", "cuda", 100000), timeout_s=300,
+                         env={"NCCL_NVLS_ENABLE": "0"})
+    replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
+
+
 @pytest.mark.multigpu
 @pytest.mark.parametrize("compressor", ["gtopk", "topk", "topk2", "none"])
 def test_two_gpu_training_matches_oracle(compressor):
