@@ -35,13 +35,14 @@ from ..settings import logger
 from . import allreducer as ar
 from . import comm
 from .compression import NoneCompressor
+from .elastic import Membership, PeerLeft
 from .flat_buffer import FlatBuffers
 
 
 class _DistributedOptimizer(torch.optim.Optimizer):
     def __init__(self, params, named_parameters, compressor, is_sparse=True, err_handler=None, layerwise_times=None,
                  sigma_scale=2.5, density=0.01, norm_clip=None, writer=None, threshold=None, overlap=True,
-                 wait_limit_ms=None):
+                 wait_limit_ms=None, membership_check_every=50):
         super(self.__class__, self).__init__(params)
         self._compressor = compressor
         self._sparse = is_sparse
@@ -83,6 +84,8 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         self._post_clip: Optional[ClipNorm] = None
         self._post_coef: Optional[torch.Tensor] = None
         self._hook_handles = []
+        self._membership = Membership.for_default_group(check_every=membership_check_every) \
+            if membership_check_every else None
         self._register_hooks()
         uniform = all(all(pg.get(k, 0) == self.param_groups[0].get(k, 0)
                           for k in ("lr", "momentum", "dampening", "weight_decay", "nesterov"))
@@ -130,8 +133,29 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             self._allreducer.reduce_group(gi)
 
     # -- public API ---------------------------------------------------------------
+    def pre_iteration(self) -> None:
+        """Host-side look at the job's membership before anything of the next
+        iteration is launched.  If a peer has left, the trainer's ``err_handler``
+        is told the new world size and GTopkTimeout is raised here, on the host,
+        instead of a device-side wait running out later."""
+        m = self._membership
+        if m is None or self.capturing:
+            return
+        try:
+            m.check(self._allreducer.train_iter)
+        except PeerLeft as exc:
+            a = self._allreducer
+            a._failed = str(exc)
+            logger.error("membership: %s", exc)
+            try:
+                a._err_callback(max(a.size() - len(exc.ranks), 1), a.rank())
+            except Exception:
+                logger.exception("err_callback raised")
+            raise ar.GTopkTimeout(str(exc)) from exc
+
     def zero_grad(self, set_to_none: bool = False):
         """Clears the flat gradient buffer with one fill; ``p.grad`` stay views."""
+        self.pre_iteration()
         self._flat.zero_grad()
         self._materialized = False
 
@@ -258,6 +282,8 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         self._allreducer.check_status()
 
     def stop(self):
+        if self._membership is not None:
+            self._membership.leave()
         self._allreducer.stop()
         for h in self._hook_handles:
             h.remove()
@@ -282,13 +308,13 @@ class _DistributedOptimizer(torch.optim.Optimizer):
 
 def DistributedOptimizer(optimizer, named_parameters=None, compression=NoneCompressor, is_sparse=False,
                          err_handler=None, layerwise_times=None, sigma_scale=2.5, density=0.1, norm_clip=None,
-                         writer=None, threshold=None, overlap=True, wait_limit_ms=None):
+                         writer=None, threshold=None, overlap=True, wait_limit_ms=None, membership_check_every=50):
     """Wrap ``optimizer``.  The returned object is an instance of a subclass of
     ``type(optimizer)`` that carries the methods above."""
     cls = type(optimizer.__class__.__name__, (optimizer.__class__,), dict(_DistributedOptimizer.__dict__))
     return cls(optimizer.param_groups, named_parameters, compression, is_sparse, err_handler, layerwise_times,
                sigma_scale=sigma_scale, density=density, norm_clip=norm_clip, writer=writer, threshold=threshold,
-               overlap=overlap, wait_limit_ms=wait_limit_ms)
+               overlap=overlap, wait_limit_ms=wait_limit_ms, membership_check_every=membership_check_every)
 
 
 def rank():

@@ -1,0 +1,96 @@
+"""Host-side membership: who is still in the job.
+
+The reference sets ``MPI.ERRORS_RETURN`` and accepts an ``err_handler`` that it
+never calls (allreducer.py:173-174,202,212; gtopk_trainer.py:42-44).  Here a
+rank that leaves between two iterations says so in the job's key-value store,
+and every rank looks at the store before it launches the next exchange, so a
+departure is noticed on the host in well under a second instead of through a
+device-side wait running out.  A rank that dies without saying goodbye is
+caught by its heartbeat going stale, and, as the last resort, by the bounded
+waits of the exchange itself.
+"""
+from __future__ import annotations
+
+import time
+from typing import List, Optional
+
+import torch.distributed as dist
+
+
+class PeerLeft(RuntimeError):
+    """One or more ranks left the job (or stopped beating)."""
+
+    def __init__(self, ranks: List[int], why: str):
+        super().__init__("ranks %s %s" % (ranks, why))
+        self.ranks = ranks
+
+
+def default_store():
+    """The key-value store behind the default process group, or None."""
+    if not dist.is_initialized():
+        return None
+    try:
+        from torch.distributed.distributed_c10d import _get_default_store
+        return dist.PrefixStore("gtopk_membership/", _get_default_store())
+    except Exception:  # a build without that accessor: no membership service
+        return None
+
+
+class Membership:
+    def __init__(self, store, rank: int, world: int, stale_after_s: float = 60.0, check_every: int = 10):
+        self.store, self.rank, self.world = store, rank, world
+        self.stale_after_s, self.check_every = stale_after_s, max(int(check_every), 1)
+        self._calls = 0
+        self._left_sent = False
+        if store is not None:
+            self.beat(0)
+
+    @classmethod
+    def for_default_group(cls, **kw) -> Optional["Membership"]:
+        store = default_store()
+        if store is None or dist.get_world_size() < 2:
+            return None
+        return cls(store, dist.get_rank(), dist.get_world_size(), **kw)
+
+    # -- this rank --------------------------------------------------------------------------
+    def beat(self, step: int) -> None:
+        self.store.set("hb/%d" % self.rank, "%d:%.3f" % (step, time.time()))
+
+    def leave(self) -> None:
+        """Announce an orderly departure (call between iterations, nothing in flight)."""
+        if not self._left_sent and self.store is not None:
+            try:
+                self.store.set("left/%d" % self.rank, "1")
+            except Exception:
+                pass  # the store's host may already be gone at shutdown
+            self._left_sent = True
+
+    # -- the others ---------------------------------------------------------------------------
+    def departed(self) -> List[int]:
+        return [q for q in range(self.world) if q != self.rank and self.store.check(["left/%d" % q])]
+
+    def stale(self, now: Optional[float] = None) -> List[int]:
+        now = time.time() if now is None else now
+        out = []
+        for q in range(self.world):
+            if q == self.rank or not self.store.check(["hb/%d" % q]):
+                continue
+            stamp = float(self.store.get("hb/%d" % q).decode().split(":")[1])
+            if now - stamp > self.stale_after_s:
+                out.append(q)
+        return out
+
+    def check(self, step: int, force: bool = False) -> None:
+        """Called at the top of an iteration, before anything is launched.
+        Every ``check_every`` calls: beat, then raise PeerLeft if somebody left
+        or went silent."""
+        self._calls += 1
+        if not force and self._calls % self.check_every:
+            return
+        self.beat(step)
+        gone = self.departed()
+        if gone:
+            raise PeerLeft(gone, "left the job")
+        silent = self.stale()
+        if silent:
+            raise PeerLeft(silent, "stopped sending heartbeats")

@@ -126,6 +126,8 @@ class GraphedStep:
                     dst.copy_(src.detach(), non_blocking=True)
         if hasattr(opt, "sync_lr"):
             opt.sync_lr()
+        if hasattr(opt, "pre_iteration"):
+            opt.pre_iteration()  # a replay runs no Python of the iteration, so look at the membership here
         g.replay()
         _native.add_launches(st["native_launches"])
         a = getattr(opt, "_allreducer", None)

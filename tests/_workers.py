@@ -16,7 +16,7 @@ def _make_batch(rank, it, bs):
 
 
 def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="cpu", threshold=None):
-    """BASELINE config: ResNet-20, batch 32 per worker would be slow on CPU;
+    """Plumbing configuration: ResNet-20; batch 32 per worker would be slow on CPU,
     batch 8 keeps the same code path.  Returns the final flat parameters."""
     from gtopkssgd_b200 import settings
     from gtopkssgd_b200.models import create_net
@@ -103,6 +103,45 @@ def graphed_step_worker(rank, world, iters, compressor):
     dopt.stop()
     comm.shutdown()
     return trace
+
+
+def leaving_peer_worker(rank, world):
+    """Rank 1 leaves in an orderly way after one iteration; rank 0 must learn
+    of it on the host before launching anything of the next iteration."""
+    import time
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.models import create_net
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.allreducer import GTopkTimeout
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("CRITICAL")
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=30)
+    torch.manual_seed(0)
+    net, _ = create_net(10, "resnet20")
+    calls = []
+    opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
+    dopt = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                                density=0.001, err_handler=lambda n, r: calls.append((n, r)), wait_limit_ms=30000,
+                                membership_check_every=1)
+    crit = torch.nn.CrossEntropyLoss()
+    x, y = _make_batch(rank, 0, 4)
+    dopt.zero_grad()
+    crit(net(x), y).backward()
+    dopt.step()
+    if rank == 1:
+        dopt.stop()  # announces the departure
+        time.sleep(3.0)  # keep the store reachable while rank 0 looks
+        return "left"
+    time.sleep(1.0)
+    t0 = time.time()
+    try:
+        dopt.zero_grad()
+        return "no error"
+    except GTopkTimeout as exc:
+        return ("left-detected", round(time.time() - t0, 2), calls, str(exc))
 
 
 def failing_peer_worker(rank, world, mode):

@@ -88,3 +88,11 @@ def test_missing_peer_raises_and_calls_err_handler(mode):
     assert res0[0] == "timeout", res0
     assert res0[1] < 60
     assert res0[2] == [(1, 0)]  # err_handler(new world size, my rank)
+
+
+def test_orderly_departure_is_seen_on_the_host_before_the_next_launch():
+    out = spawn_ranks(_workers.leaving_peer_worker, 2, timeout_s=240)
+    assert out[1] == "left"
+    kind, seconds, calls, msg = out[0]
+    assert kind == "left-detected" and seconds < 2.0  # far below the 30 s wait limit
+    assert calls == [(1, 0)] and "[1]" in msg
