@@ -128,9 +128,9 @@ struct RankBarrier {
   __device__ __forceinline__ bool sync(uint32_t where) {
     __shared__ int ok_s;
     unsigned int* const arrivals = counter ? counter : &ctrl->bar;
-    if (nctas == 1) {
+    if (nctas == 1) {  // a single CTA learns of its own failures through its shared flags
       __syncthreads();
-      return !aborted(ctrl);
+      return true;
     }
     gen += 1;
     __syncthreads();

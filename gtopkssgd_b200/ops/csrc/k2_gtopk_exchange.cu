@@ -21,28 +21,54 @@
 
 namespace gtk {
 
+constexpr int kK2Cache = 4;  // union entries each thread keeps in registers across the phases of a round
+
+struct K2Shared {
+  ExchangeShared ex;
+  unsigned int hist0[kHistBins];  // this CTA's share of the first-digit histogram, built on the fly
+};
+
+__device__ __forceinline__ void hist0_clear(K2Shared& sh) {
+  for (int i = threadIdx.x; i < kHistBins; i += kSelThreads) sh.hist0[i] = 0u;
+  __syncthreads();
+}
+// Adds this CTA's (possibly "negative", i.e. wrapped) partial counts to a global histogram.
+__device__ __forceinline__ void hist0_flush(K2Shared& sh, unsigned int* ghist) {
+  __syncthreads();
+  for (int i = threadIdx.x; i < kHistBins; i += kSelThreads) {
+    const unsigned int c = sh.hist0[i];
+    if (c) atomicAdd(&ghist[i], c);
+    sh.hist0[i] = 0u;
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(kSelThreads)
 k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsigned int P,
                   unsigned int k, unsigned int kcap, unsigned int d, unsigned long long limit_ns) {
-  __shared__ ExchangeShared sh;
+  __shared__ K2Shared sh;
+  SelectShared& ss = sh.ex.sel;
   const K2Rank& R = ranks[blockIdx.y];
   const unsigned int epoch = __ldcg(R.epoch);  // every CTA reads it before its first barrier
   const unsigned int me = rank_base + blockIdx.y;
   const unsigned int cta = blockIdx.x, nct = gridDim.x;
   const unsigned int parity = epoch & 1u;
+  const unsigned int stride = nct * kSelThreads;
+  const unsigned int lane0 = cta * kSelThreads + threadIdx.x;  // union index of this thread's trip 0
+  const bool single = nct == 1;  // the whole rank is this CTA: histograms never leave shared memory
   Ctrl* ctrl = R.ctrl;
+  int32_t* const map = R.map;
   RankBarrier bar{ctrl, nct, 0u, limit_ns};
 
   unsigned int n_sel = R.st->n_sel;
   if (n_sel > kcap) n_sel = kcap;
-  const Pair* cur = R.sel;      // current set of this rank
+  const Pair* cur = R.sel;  // current set of this rank
   unsigned int n_cur = n_sel;
-  bool cur_is_work = false;     // cur already lives in a writable work buffer
-  bool cur_mapped = false;      // map[] already describes cur
-  int cur_buf = 0;
+  int cur_buf = -1;         // -1: cur is the read-only selection of K1; else index of the work buffer
 
   unsigned int rounds = 0;
   while ((1u << rounds) < P) ++rounds;
+  hist0_clear(sh);
   trace_stamp(ctrl, 0);
 
   for (unsigned int r = 0; r < rounds; ++r) {
@@ -61,19 +87,27 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       break;
     }
     if (low != 0u) break;  // already left the tree
-    // ---- receiver
+
+    // ---- receiver.  A = current set in a writable work buffer, with map[] and the first-digit
+    // histogram describing it (built here in round 0, by the previous compaction afterwards).
     Pair* A;
-    if (!cur_is_work) {
+    const bool copied = cur_buf < 0;
+    if (copied) {
       A = R.work[0];
-      copy_and_map(A, cur, n_cur, R.map, d, cta, nct, ctrl);
+      for (unsigned int i = lane0; i < n_cur; i += stride) {
+        const Pair e = ld_pair_cg(&cur[i]);
+        st_pair(&A[i], e);
+        if ((unsigned int)e.idx < d) map[e.idx] = (int32_t)i;
+        else record_error(ctrl, ST_BOUNDS, 300);
+        atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
+      }
       cur_buf = 0;
     } else {
       A = R.work[cur_buf];
-      if (!cur_mapped) build_map(A, n_cur, R.map, d, cta, nct, ctrl);
     }
     unsigned int n_b = 0;
     trace_stamp(ctrl, 1 + 8 * r + 0);
-    if (!cta_wait_flag(sh, R.flags + flag_off(parity, r), epoch, ctrl, limit_ns, 210 + r, &n_b))
+    if (!cta_wait_flag(sh.ex, R.flags + flag_off(parity, r), epoch, ctrl, limit_ns, 210 + r, &n_b))
       return;
     trace_stamp(ctrl, 1 + 8 * r + 1);
     if (n_b > kcap) {
@@ -81,46 +115,169 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       n_b = kcap;
     }
     Pair* B = R.slots + slot_off(parity, r, kcap);
-    if (!bar.sync(230 + r)) return;  // map complete
-    trace_stamp(ctrl, 1 + 8 * r + 2);
-    probe_merge(A, n_cur, B, n_b, R.map, d, cta, nct, ctrl);
-    if (!bar.sync(240 + r)) return;  // sums complete
-    trace_stamp(ctrl, 1 + 8 * r + 3);
-    // ---- re-select the k largest magnitudes of A u live(B)
     const unsigned int n_a = n_cur;
     const unsigned int n_u = n_a + n_b;
-    auto key_at = [&](unsigned int i) -> uint32_t {
-      const Pair e = ld_pair_cg(i < n_a ? &A[i] : &B[i - n_a]);
-      return e.idx < 0 ? 0xffffffffu : mag_key(e.val);
-    };
-    Threshold th;
-    if (!radix_select_kth(sh.sel, bar, cta, nct, n_u, k, ctrl->hist[r], key_at, &th, 250 + 10 * r))
-      return;
-    trace_stamp(ctrl, 1 + 8 * r + 4);
-    Pair* OUT = R.work[cur_buf ^ 1];
-    int32_t* map = R.map;
-    auto on_placed = [&](Pair e, unsigned int pos) { map[e.idx] = (int32_t)pos; };
-    StagedAppender app{&sh.sel, OUT, &ctrl->cursor[r], kcap, ctrl};
-    app.begin();
-    const unsigned int stride = nct * kSelThreads;
     const unsigned int trips = (n_u + stride - 1) / stride;
-    for (unsigned int t = 0; t < trips; ++t) {
-      const unsigned int i = t * stride + cta * kSelThreads + threadIdx.x;
-      if (i < n_u) {
-        const Pair e = ld_pair_cg(i < n_a ? &A[i] : &B[i - n_a]);
-        if (e.idx >= 0 && passes_threshold(mag_key(e.val), th, &ctrl->tie[r])) app.put(e);
+    // A and map must be complete: after the copy above that needs a barrier, after a previous
+    // round its closing barrier already gave it
+    if (copied && !bar.sync(230 + r)) return;
+    trace_stamp(ctrl, 1 + 8 * r + 2);
+
+    // ---- probe: every thread joins its own B entries against A (sum on shared indices) and
+    // keeps them in registers; three dependent loads, issued level by level.
+    Pair c[kK2Cache];
+    unsigned int pm[kK2Cache];
+    auto join = [&](Pair& e, unsigned int p, unsigned int j) {
+      bool matched = false;
+      if (p < n_a) {
+        const Pair a = ld_pair_cg(&A[p]);
+        if (a.idx == e.idx) {
+          const float nv = a.val + e.val;
+          A[p].val = nv;  // A[p] belongs to another thread's sweep: goes through memory
+          atomicAdd(&sh.hist0[mag_key(a.val) >> 20], 0xffffffffu);
+          atomicAdd(&sh.hist0[mag_key(nv) >> 20], 1u);
+          B[j].idx = -1;
+          e.idx = -1;
+          matched = true;
+        }
       }
+      if (!matched) atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
+    };
+#pragma unroll
+    for (int t = 0; t < kK2Cache; ++t) {
+      const unsigned int i = (unsigned int)t * stride + lane0;
+      c[t].idx = -1;
+      c[t].val = 0.f;
+      if ((unsigned int)t < trips && i >= n_a && i < n_u) c[t] = ld_pair_cg(&B[i - n_a]);
+    }
+#pragma unroll
+    for (int t = 0; t < kK2Cache; ++t) {
+      pm[t] = 0xffffffffu;
+      if (c[t].idx >= 0) {
+        if ((unsigned int)c[t].idx < d) {
+          pm[t] = (unsigned int)__ldcg(&map[c[t].idx]);
+        } else {
+          record_error(ctrl, ST_BOUNDS, 302);
+          B[(unsigned int)t * stride + lane0 - n_a].idx = -1;
+          c[t].idx = -1;
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < kK2Cache; ++t)
+      if (c[t].idx >= 0) join(c[t], pm[t], (unsigned int)t * stride + lane0 - n_a);
+    for (unsigned int t = kK2Cache; t < trips; ++t) {  // entries beyond the register cache
+      const unsigned int i = t * stride + lane0;
+      if (i >= n_a && i < n_u) {
+        Pair e = ld_pair_cg(&B[i - n_a]);
+        if ((unsigned int)e.idx >= d) {
+          record_error(ctrl, ST_BOUNDS, 302);
+          B[i - n_a].idx = -1;
+        } else {
+          join(e, (unsigned int)__ldcg(&map[e.idx]), i - n_a);
+        }
+      }
+    }
+    if (!single) hist0_flush(sh, ctrl->hist[r][0]);
+    if (!bar.sync(240 + r)) return;  // sums and first-digit histogram complete
+    trace_stamp(ctrl, 1 + 8 * r + 3);
+
+    // ---- every thread now loads its A entries (with the merged values) next to its B entries
+#pragma unroll
+    for (int t = 0; t < kK2Cache; ++t) {
+      const unsigned int i = (unsigned int)t * stride + lane0;
+      if ((unsigned int)t < trips && i < n_a) c[t] = ld_pair_cg(&A[i]);
+    }
+    auto entry = [&](unsigned int t) -> Pair {  // entry of trip t >= kK2Cache, from memory
+      const unsigned int i = t * stride + lane0;
+      Pair e;
+      e.idx = -1;
+      e.val = 0.f;
+      if (i < n_u) e = ld_pair_cg(i < n_a ? &A[i] : &B[i - n_a]);
+      return e;
+    };
+
+    // ---- re-select: the first digit is known from the histogram built on the fly
+    Threshold th;
+    th.select_all = false;
+    th.key = 0u;
+    th.quota = 0u;
+    find_digit_in<kHistBins>(ss, single ? sh.hist0 : ctrl->hist[r][0], k, single);
+    const bool all = ss.res_total <= k;
+    uint32_t prefix = ss.res_digit;
+    unsigned int k_rem = ss.res_krem;
+    __syncthreads();
+    if (single) hist0_clear(sh);  // from here on it collects the next round's first digits
+    if (all) {
+      th.select_all = true;
+    } else {
+      // pass 1: bits 19..10 of the entries whose first digit is the threshold digit
+      smem_hist_clear(ss);
+#pragma unroll
+      for (int t = 0; t < kK2Cache; ++t)
+        if (c[t].idx >= 0 && (mag_key(c[t].val) >> 20) == prefix)
+          atomicAdd(&ss.hist[(mag_key(c[t].val) >> 10) & 1023u], 1u);
+      for (unsigned int t = kK2Cache; t < trips; ++t) {
+        const Pair e = entry(t);
+        if (e.idx >= 0 && (mag_key(e.val) >> 20) == prefix)
+          atomicAdd(&ss.hist[(mag_key(e.val) >> 10) & 1023u], 1u);
+      }
+      if (!single) smem_hist_flush(ss, ctrl->hist[r][1], 1024);
+      if (!bar.sync(250 + 10 * r)) return;
+      find_digit<1024>(ss, ctrl->hist[r][1], k_rem, single);
+      prefix = (prefix << 10) | ss.res_digit;
+      k_rem = ss.res_krem;
+      __syncthreads();
+      // pass 2: bits 9..0
+      smem_hist_clear(ss);
+#pragma unroll
+      for (int t = 0; t < kK2Cache; ++t)
+        if (c[t].idx >= 0 && (mag_key(c[t].val) >> 10) == prefix)
+          atomicAdd(&ss.hist[mag_key(c[t].val) & 1023u], 1u);
+      for (unsigned int t = kK2Cache; t < trips; ++t) {
+        const Pair e = entry(t);
+        if (e.idx >= 0 && (mag_key(e.val) >> 10) == prefix) atomicAdd(&ss.hist[mag_key(e.val) & 1023u], 1u);
+      }
+      if (!single) smem_hist_flush(ss, ctrl->hist[r][2], 1024);
+      if (!bar.sync(251 + 10 * r)) return;
+      find_digit<1024>(ss, ctrl->hist[r][2], k_rem, single);
+      th.key = (prefix << 10) | ss.res_digit;
+      th.quota = ss.res_krem;
+      __syncthreads();
+    }
+    trace_stamp(ctrl, 1 + 8 * r + 4);
+
+    // ---- compaction of the winners into the other work buffer; the table and the first-digit
+    // histogram of the next round are built on the way
+    Pair* OUT = R.work[cur_buf ^ 1];
+    auto on_placed = [&](Pair e, unsigned int pos) { map[e.idx] = (int32_t)pos; };
+    StagedAppender app{&ss, OUT, &ctrl->cursor[r], kcap, ctrl};
+    app.begin();
+    auto consider = [&](const Pair& e) {
+      if (e.idx >= 0 && passes_threshold(mag_key(e.val), th, &ctrl->tie[r])) {
+        app.put(e);
+        atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
+      }
+    };
+#pragma unroll
+    for (int t = 0; t < kK2Cache; ++t) {
+      if ((unsigned int)t < trips) {
+        consider(c[t]);
+        app.end_tile(on_placed);
+      }
+    }
+    for (unsigned int t = kK2Cache; t < trips; ++t) {
+      consider(entry(t));
       app.end_tile(on_placed);
     }
     app.flush(on_placed);
+    if (!single && r + 1 < rounds) hist0_flush(sh, ctrl->hist[r + 1][0]);
     if (!bar.sync(290 + r)) return;  // OUT and its cursor complete
     trace_stamp(ctrl, 1 + 8 * r + 5);
     n_cur = __ldcg(&ctrl->cursor[r]);
     if (n_cur > kcap) n_cur = kcap;
     cur_buf ^= 1;
     cur = R.work[cur_buf];
-    cur_is_work = true;
-    cur_mapped = true;
   }
 
   // ---- broadcast of the global set (rank 0 pushes to everyone, itself included)
@@ -136,7 +293,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     if (cta == 0 && threadIdx.x < P && threadIdx.x > 0)  // one releasing thread per destination
       release_flag(R.peer_flags[threadIdx.x] + flag_off(parity, kFlagBcast), epoch, n_cur);
   } else {
-    if (!cta_wait_flag(sh, R.flags + flag_off(parity, kFlagBcast), epoch, ctrl, limit_ns, 410, &n_g))
+    if (!cta_wait_flag(sh.ex, R.flags + flag_off(parity, kFlagBcast), epoch, ctrl, limit_ns, 410, &n_g))
       return;
     if (n_g > kcap) {
       record_error(ctrl, ST_CAPACITY, 411);
@@ -145,10 +302,10 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
   }
   // ---- residual put-back of S_local \ S_global
   trace_stamp(ctrl, 40);
-  build_map(G, n_g, R.map, d, cta, nct, ctrl);
+  build_map(G, n_g, map, d, cta, nct, ctrl);
   if (!bar.sync(420)) return;
   trace_stamp(ctrl, 41);
-  put_back(R.sel, n_sel, G, n_g, R.map, R.resid, d, cta, nct);
+  put_back(R.sel, n_sel, G, n_g, map, R.resid, d, cta, nct);
   if (cta == 0 && threadIdx.x == 0) {
     *R.n_global = n_g;
     *R.epoch = epoch + 1u;  // safe: all CTAs passed the barrier above, hence read the old value
@@ -238,7 +395,8 @@ extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, uns
   if ((int)(nranks * nctas) > maxco) return GTK_ERR_ARG;
   unsigned int rounds = 0;
   while ((1u << rounds) < P) ++rounds;
-  const size_t clear_bytes = offsetof(Ctrl, hist) + (size_t)rounds * sizeof(((Ctrl*)0)->hist[0]);
+  // header + trace + one histogram set per round, plus the first-digit histogram of the round after
+  const size_t clear_bytes = offsetof(Ctrl, hist) + (size_t)(rounds + 1) * sizeof(((Ctrl*)0)->hist[0]);
   for (unsigned int i = 0; i < nranks; ++i)
     if (cudaMemsetAsync(ctrl_dev[i], 0, clear_bytes, stream) != cudaSuccess) return GTK_ERR_CUDA;
   const K2Rank* ranks = (const K2Rank*)ranks_dev;

@@ -45,11 +45,11 @@ __device__ __forceinline__ void smem_hist_flush(SelectShared& s, unsigned int* g
 // finds the digit D with count(bins > D) < k_rem <= count(bins >= D).
 // Results are left in shared memory: res_digit, res_krem (k_rem minus the count
 // above D), res_total (all entries), res_equal (count in bin D).
-// With local = true the counts are read from the CTA's own shared histogram
-// (single-CTA ranks never touch the global copy).
+// counts: the histogram to scan; in_smem says whether it is a shared-memory
+// array of this CTA (single-CTA ranks never touch a global copy) or a global one.
 template <int NBINS>
-__device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* ghist,
-                                           unsigned int k_rem, bool local) {
+__device__ __forceinline__ void find_digit_in(SelectShared& s, const unsigned int* counts,
+                                              unsigned int k_rem, bool in_smem) {
   constexpr int BPT = NBINS / kSelThreads;
   static_assert(BPT >= 1, "bins per thread");
   const int t = threadIdx.x;
@@ -57,7 +57,7 @@ __device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* 
   unsigned int mine = 0;
 #pragma unroll
   for (int j = 0; j < BPT; ++j) {
-    c[j] = local ? s.hist[t * BPT + j] : __ldcg(&ghist[t * BPT + j]);
+    c[j] = in_smem ? counts[t * BPT + j] : __ldcg(&counts[t * BPT + j]);
     mine += c[j];
   }
   // inclusive suffix sum over threads (higher thread = higher bins)
@@ -93,6 +93,12 @@ __device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* 
     }
   }
   __syncthreads();
+}
+
+template <int NBINS>
+__device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* ghist,
+                                           unsigned int k_rem, bool local) {
+  find_digit_in<NBINS>(s, local ? s.hist : ghist, k_rem, local);
 }
 
 // Radix select of the k-th largest magnitude over `n` logical entries, where
