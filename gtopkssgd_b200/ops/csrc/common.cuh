@@ -124,12 +124,21 @@ struct RankBarrier {
   unsigned int gen;
   uint64_t limit_ns;
   unsigned int* counter = nullptr;  // arrival counter; nullptr: ctrl->bar
+  bool cluster = false;             // the rank's CTAs form one thread-block cluster: hardware barrier
 
   __device__ __forceinline__ bool sync(uint32_t where) {
     __shared__ int ok_s;
     unsigned int* const arrivals = counter ? counter : &ctrl->bar;
     if (nctas == 1) {  // a single CTA learns of its own failures through its shared flags
       __syncthreads();
+      return true;
+    }
+    if (cluster) {
+      // Cluster-scope release/acquire: global and shared writes made before the barrier by any
+      // CTA of the cluster are visible to all of them after it.  The hardware barrier waits only
+      // for threads that have not exited, so a CTA that gave up on a flag wait does not block it.
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
       return true;
     }
     gen += 1;

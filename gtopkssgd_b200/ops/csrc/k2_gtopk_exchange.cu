@@ -45,7 +45,8 @@ __device__ __forceinline__ void hist0_flush(K2Shared& sh, unsigned int* ghist) {
 
 __global__ void __launch_bounds__(kSelThreads)
 k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsigned int P,
-                  unsigned int k, unsigned int kcap, unsigned int d, unsigned long long limit_ns) {
+                  unsigned int k, unsigned int kcap, unsigned int d, unsigned long long limit_ns,
+                  int use_cluster) {
   __shared__ K2Shared sh;
   SelectShared& ss = sh.ex.sel;
   const K2Rank& R = ranks[blockIdx.y];
@@ -58,7 +59,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
   const bool single = nct == 1;  // the whole rank is this CTA: histograms never leave shared memory
   Ctrl* ctrl = R.ctrl;
   int32_t* const map = R.map;
-  RankBarrier bar{ctrl, nct, 0u, limit_ns};
+  RankBarrier bar{ctrl, nct, 0u, limit_ns, nullptr, use_cluster != 0};
 
   unsigned int n_sel = R.st->n_sel;
   if (n_sel > kcap) n_sel = kcap;
@@ -382,12 +383,48 @@ static int k2_max_coresident(void* fn) {
   return cached;
 }
 
+// Largest cluster (CTAs of one rank joined by the hardware barrier) that `nranks` ranks can hold
+// co-resident on this device; 0 if clusters cannot be used.  Cached per (nranks, nctas).
+static bool k2_cluster_fits(unsigned int nranks, unsigned int nctas) {
+  static int cache[kMaxPeers + 1][17] = {};  // 0 unknown, 1 yes, 2 no
+  if (nctas < 2 || nctas > 16 || (nctas & (nctas - 1)) || nranks > (unsigned int)kMaxPeers) return false;
+  int& c = cache[nranks][nctas];
+  if (c) return c == 1;
+  c = 2;
+  const DeviceInfo* di = gtk_device_info();
+  if (!di || !di->cluster) return false;
+  if (nctas > 8 && cudaFuncSetAttribute((const void*)k2_gtopk_exchange,
+                                        cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nctas, nranks);
+  cfg.blockDim = dim3(kSelThreads);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nctas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int nclusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&nclusters, (const void*)k2_gtopk_exchange, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  if (nclusters >= (int)nranks) c = 1;
+  return c == 1;
+}
+
 // ranks_dev: device array of nranks_in_launch K2Rank descriptors (1 in production).
 // ctrl_dev[i]: control block of each of those ranks (cleared here).
+// use_cluster: 1 = join the CTAs of a rank into one thread-block cluster (hardware barrier) when
+// nctas is 2, 4, 8 or 16 and the device can hold the clusters; 0 = software barrier.
 extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, unsigned int nranks,
                                unsigned int rank_base, unsigned int P, unsigned int k,
                                unsigned int kcap, unsigned int d, unsigned int nctas,
-                               unsigned long long limit_ns, void* stream_) {
+                               unsigned long long limit_ns, int use_cluster, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (P < 2 || (P & (P - 1)) != 0 || P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
   if (k == 0 || k > kcap || nranks == 0 || nctas == 0) return GTK_ERR_ARG;
@@ -400,9 +437,28 @@ extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, uns
   for (unsigned int i = 0; i < nranks; ++i)
     if (cudaMemsetAsync(ctrl_dev[i], 0, clear_bytes, stream) != cudaSuccess) return GTK_ERR_CUDA;
   const K2Rank* ranks = (const K2Rank*)ranks_dev;
-  void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &limit_ns};
-  cudaError_t e = cudaLaunchCooperativeKernel((void*)k2_gtopk_exchange, dim3(nctas, nranks),
-                                              dim3(kSelThreads), args, 0, stream);
+  int cluster = (use_cluster && k2_cluster_fits(nranks, nctas)) ? 1 : 0;
+  void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &limit_ns, &cluster};
+  cudaError_t e;
+  if (cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nctas, nranks);
+    cfg.blockDim = dim3(kSelThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeCooperative;  // several emulated ranks wait on one another
+    attr[1].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = nranks > 1 ? 2 : 1;  // one cluster is co-scheduled by the hardware anyway
+    e = cudaLaunchKernelExC(&cfg, (const void*)k2_gtopk_exchange, args);
+  } else {
+    e = cudaLaunchCooperativeKernel((void*)k2_gtopk_exchange, dim3(nctas, nranks), dim3(kSelThreads),
+                                    args, 0, stream);
+  }
   gtk_count_launch(1);
   if (e != cudaSuccess) return GTK_ERR_CUDA;
   return GTK_OK;

@@ -157,18 +157,27 @@ def _desc_array(ranks: Sequence[ExchangeRank]) -> torch.Tensor:
 
 
 def default_nctas(k: int, nranks: int = 1, sms: int = 148) -> int:
-    """CTAs per rank for the exchange kernels.  Small sets run in one CTA (no
-    grid barrier, shared-memory histograms); larger ones take about one CTA per
-    1024 union entries so that every thread handles two entries per sweep
-    (measured on B200: 1 CTA up to k = 1.5 K, 64 CTAs at k = 25 K, 128 at k >= 66 K)."""
-    if 2 * k <= 3072:
+    """CTAs per rank for the exchange kernels, from a sweep on B200.
+
+    * up to 3 K union entries: one CTA (no inter-CTA barrier, histograms stay in
+      shared memory; about 10 us per tree round);
+    * up to 64 K union entries: a power-of-two cluster of 2..16 CTAs joined by
+      the hardware cluster barrier, about four entries per thread in registers;
+    * above: one CTA per 1024 entries (up to 128) with the software barrier."""
+    n_u = 2 * k
+    if n_u <= 3072:
         return 1
-    n = min(128, (2 * k + 1023) // 1024)
+    if n_u <= 65536:
+        n = 2
+        while n < 16 and n * 2048 < n_u:
+            n *= 2
+        return n
+    n = min(128, (n_u + 1023) // 1024)
     return max(1, min(n, sms // max(nranks, 1)))
 
 
 def launch_gtopk(ranks: Sequence[ExchangeRank], desc: torch.Tensor, rank_base: int, world: int, k: int,
-                 nctas: Optional[int] = None, limit_ms: float = 5000.0) -> None:
+                 nctas: Optional[int] = None, limit_ms: float = 5000.0, use_cluster: bool = True) -> None:
     """Enqueue one gTop-k exchange.  ``ranks`` are the ranks served by this
     launch (one in production, all P when emulated); ``desc`` is their
     concatenated device descriptor array."""
@@ -178,7 +187,7 @@ def launch_gtopk(ranks: Sequence[ExchangeRank], desc: torch.Tensor, rank_base: i
         nctas = default_nctas(k, len(ranks))
     ctrls = (C.c_void_p * len(ranks))(*[C.c_void_p(r.ctrl.data_ptr()) for r in ranks])
     code = L.gtk_k2_exchange(desc.data_ptr(), ctrls, len(ranks), rank_base, world, k, r0.kcap, r0.numel,
-                             nctas, int(limit_ms * 1e6), current_stream_handle(r0.resid.device))
+                             nctas, int(limit_ms * 1e6), int(use_cluster), current_stream_handle(r0.resid.device))
     _lib.check(code, "gtk_k2_exchange")
 
 

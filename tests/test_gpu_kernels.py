@@ -230,7 +230,8 @@ def _read_gout(rank, parity):
 
 
 @pytest.mark.parametrize("P", [2, 4, 8])
-@pytest.mark.parametrize("d,k,nctas", [(4096, 8, 1), (50000, 50, 1), (300000, 3000, 4), (2_000_000, 20000, 8)])
+@pytest.mark.parametrize("d,k,nctas", [(4096, 8, 1), (50000, 50, 1), (300000, 3000, 4), (2_000_000, 20000, 8),
+                                       (2_000_000, 20000, 12)])  # 1 CTA; clusters of 4 and 8; software barrier
 def test_k2_gtopk_exchange_emulated(P, d, k, nctas):
     from gtopkssgd_b200.ops import exchange as ex
     torch.manual_seed(100 * P + k)
