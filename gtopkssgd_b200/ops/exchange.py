@@ -157,22 +157,25 @@ def _desc_array(ranks: Sequence[ExchangeRank]) -> torch.Tensor:
 
 
 def default_nctas(k: int, nranks: int = 1, sms: int = 148) -> int:
-    """CTAs per rank for the exchange kernels, from a sweep on B200.
+    """CTAs per rank for the exchange kernels, from sweeps on B200 (in-kernel
+    time of one tree round + broadcast + put-back):
 
     * up to 3 K union entries: one CTA (no inter-CTA barrier, histograms stay in
-      shared memory; about 10 us per tree round);
-    * up to 64 K union entries: a power-of-two cluster of 2..16 CTAs joined by
-      the hardware cluster barrier, about four entries per thread in registers;
-    * above: one CTA per 1024 entries (up to 128) with the software barrier."""
+      shared memory; about 10 us per round);
+    * up to 32 K union entries: a power-of-two cluster of 2..16 CTAs joined by
+      the hardware cluster barrier, about 1024 entries per CTA (k = 4 000: 19 us
+      against 25 us with the software barrier; k = 14 700: 23 us against 27 us);
+    * above: one CTA per 768 entries (up to 128) with the software barrier
+      (k = 25 600: 26 us with 64 CTAs against 33 us with a cluster of 16)."""
     n_u = 2 * k
     if n_u <= 3072:
         return 1
-    if n_u <= 65536:
+    if n_u <= 32768:
         n = 2
-        while n < 16 and n * 2048 < n_u:
+        while n < 16 and n * 1024 < n_u:
             n *= 2
         return n
-    n = min(128, (n_u + 1023) // 1024)
+    n = min(128, (n_u + 767) // 768)
     return max(1, min(n, sms // max(nranks, 1)))
 
 
