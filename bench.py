@@ -43,6 +43,21 @@ MODEL_DEFAULTS = {  # dataset, per-GPU batch, lr
 }
 
 
+def _claim_stdout() -> int:
+    """Keep stdout for the one JSON line: everything else that writes to file
+    descriptor 1 during the run (library banners such as NCCL's version line)
+    goes to stderr.  Returns a descriptor of the original stdout."""
+    sys.stdout.flush()
+    real = os.dup(1)
+    os.dup2(2, 1)
+    return real
+
+
+def _emit(real_stdout: int, obj) -> None:
+    sys.stdout.flush()
+    os.write(real_stdout, (json.dumps(obj) + "\n").encode())
+
+
 def reference_arm(args):
     reason = ("reference is not installable (no setup.py/pyproject.toml) and imports mpi4py, horovod and "
               "tensorboardX at module load, none of which exist in this image; it is also Python-2-only "
@@ -71,6 +86,7 @@ def main():
         return reference_arm(args)
     if args.warmup < 3:
         args.warmup = 3
+    real_stdout = _claim_stdout()
 
     import torch
     from gtopkssgd_b200 import settings
@@ -84,7 +100,7 @@ def main():
     settings.PIN_DENSITY = True  # the named configs fix the density at 0.001 from the first step
     settings.logger.setLevel("WARNING")
     if not torch.cuda.is_available():
-        print(json.dumps({"error": "bench.py needs a CUDA device"}), flush=True)
+        _emit(real_stdout, {"error": "bench.py needs a CUDA device"})
         return 1
     torch.backends.cudnn.benchmark = True
     torch.backends.cudnn.allow_tf32 = False          # strict fp32, as the reference trains
@@ -96,7 +112,7 @@ def main():
     rank, world = comm.rank(), comm.size()
     if world != args.gpus:
         if rank == 0:
-            print(json.dumps({"error": "--gpus %d but world size is %d" % (args.gpus, world)}), flush=True)
+            _emit(real_stdout, {"error": "--gpus %d but world size is %d" % (args.gpus, world)})
         return 1
 
     dataset, bs, lr = MODEL_DEFAULTS[args.model]
@@ -224,7 +240,7 @@ def main():
         "gpu_launches": int(launches),
     }
     if rank == 0:
-        print(json.dumps(out), flush=True)
+        _emit(real_stdout, out)
     optimizer.stop()
     comm.shutdown()
     return 0
