@@ -214,6 +214,10 @@ class AllReducer:
         self.wait_limit_ms = float(wait_limit_ms if wait_limit_ms is not None else settings.WAIT_LIMIT_MS)
         cname = getattr(compression, "name", "none") if compression is not None else "none"
         self.mode = cname if self._sparse else "none"
+        world = comm.size()
+        if self.mode == "gtopk" and world & (world - 1):
+            raise ValueError("gTop-k pairs ranks in a recursive-doubling tree and needs a power-of-two number of "
+                             "workers (got %d); use the 'topk' or 'topk2' compressor otherwise" % world)
         logger.info("density: %f", self._density)
         named = list(named_parameters)
         self._named_parameters = dict(named)

@@ -340,3 +340,75 @@ def test_log_parser_reads_trainer_lines(tmp_path):
     assert log.val_acc == [0.412] and log.densities == [0.001]
     assert mean_speed(log, skip=0) == 640.0
     assert log.profiling[0]["compression"] == pytest.approx(1.2e-4) and log.profiling[0]["size"] == 269722
+
+
+def test_norm_clip_before_compression_and_momentum_correction(monkeypatch):
+    """norm_clip scales the merged gradient to sqrt(1/P)*norm_clip before it is
+    sparsified (allreducer.py:531-538 in the reference); momentum correction
+    sparsifies the velocity instead of the raw gradient."""
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+    torch.manual_seed(0)
+    net, _ = create_net(10, "mnistnet")
+    net.eval()
+    opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
+    d = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                             density=1.0, norm_clip=0.5)
+    x = torch.randn(4, 1, 28, 28)
+    d.zero_grad()
+    net(x).sum().backward()
+    raw = d._flat.grad[:d._flat.numel].clone()
+    assert float(raw.norm()) > 0.5
+    idx, val = d._allreducer.engines[0].selector.pairs()  # density 1: everything selected, after clipping
+    assert float(val.norm()) == pytest.approx(0.5, rel=1e-4)
+    d.step()
+    d.stop()
+    # momentum correction: velocity buffer is updated in the hook and replaces the gradient
+    net2, _ = create_net(10, "mnistnet")
+    net2.eval()
+    opt2 = torch.optim.SGD(net2.parameters(), lr=0.1, momentum=0.9)
+    d2 = DistributedOptimizer(opt2, net2.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                              density=1.0)
+    d2.momentum_correction = True
+    p0 = d2._flat.param.clone()
+    for _ in range(2):
+        d2.zero_grad()
+        net2(x).sum().backward()
+        d2.step()
+    assert float(d2._flat.momentum.abs().sum()) > 0
+    assert not torch.equal(d2._flat.param, p0)
+    d2.stop()
+
+
+def test_profiling_norm_diagnostic(monkeypatch):
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+    monkeypatch.setattr(settings, "PROFILING_NORM", True)
+    net, _ = create_net(10, "mnistnet")
+    net.eval()
+    opt = torch.optim.SGD(net.parameters(), lr=0.01)
+    d = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                             density=0.01)
+    d.zero_grad()
+    net(torch.randn(4, 1, 28, 28)).sum().backward()
+    d.step()
+    (gtopk_norm, randk_norm, upbound, xnorm, std), = d._allreducer._profiling_norms
+    assert 0 <= gtopk_norm <= randk_norm <= xnorm  # top-k keeps at least as much mass as random-k
+    d.stop()
+
+
+@pytest.mark.parametrize("dnn,dataset,extra", [("mnistnet", "mnist", []), ("lstm", "ptb", ["--num-steps", "5"])])
+def test_single_gpu_cli_smoke(tmp_path, monkeypatch, dnn, dataset, extra):
+    from gtopkssgd_b200.trainer import dl_trainer
+    monkeypatch.chdir(tmp_path)
+    dl_trainer.main(["--dnn", dnn, "--dataset", dataset, "--data-dir", "synthetic", "--batch-size", "4",
+                     "--lr", "0.01", "--max-epochs", "1", "--max-iters", "2"] + extra)
+    assert any(f.endswith(".log") for _, _, fs in os.walk(tmp_path / "logs") for f in fs)
+
+
+def test_gtopk_cli_smoke_an4_synthetic(tmp_path, monkeypatch):
+    from gtopkssgd_b200.trainer import gtopk_trainer
+    monkeypatch.chdir(tmp_path)
+    gtopk_trainer.main(["--dnn", "lstman4", "--dataset", "an4", "--data-dir", "synthetic", "--batch-size", "2",
+                        "--lr", "0.0003", "--compression", "--compressor", "gtopk", "--density", "0.001",
+                        "--max-epochs", "1", "--max-iters", "1"])
+    logdir = tmp_path / "logs"
+    assert any("lstman4-n1-bs2-lr0.0003-ns1-sg2.50-ds0.001" in dp for dp, _, _ in os.walk(logdir))
