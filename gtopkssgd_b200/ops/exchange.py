@@ -22,6 +22,8 @@ from . import lib as _lib
 from .select import TopkSelector, current_stream_handle
 
 MAX_PEERS = 16
+GUARD_BYTES = 256      # canary band before and after every symmetric region
+GUARD_PATTERN = 0xA5
 
 
 def symm_layout(kcap: int, with_allgather: bool) -> Tuple[int, int, int, int, int]:
@@ -33,21 +35,42 @@ def symm_layout(kcap: int, with_allgather: bool) -> Tuple[int, int, int, int, in
 class SymmetricRegion:
     """One rank's peer-visible buffer and the peers' mapped addresses."""
 
-    def __init__(self, rank: int, world: int, nbytes: int, local_ptr: int, peer_ptrs: Sequence[int], owner=None,
-                 ipc: bool = False):
+    def __init__(self, rank: int, world: int, nbytes: int, raw_ptr: int, raw_peer_ptrs: Sequence[int], device,
+                 owner=None, ipc: bool = False):
+        """``raw_ptr`` / ``raw_peer_ptrs`` address allocations of nbytes + 2 * GUARD_BYTES; the usable region
+        starts GUARD_BYTES in.  Both guard bands of the local allocation are filled with a pattern that no
+        kernel may touch; ``guards_intact()`` re-reads them (a peer or a local kernel that stored outside
+        its slots shows up there instead of corrupting a neighbour silently)."""
         self.rank, self.world, self.nbytes = rank, world, nbytes
-        self.local_ptr = int(local_ptr)
-        self.peer_ptrs = [int(p) for p in peer_ptrs]
+        self._raw_ptr = int(raw_ptr)
+        self._raw_peers = [int(p) for p in raw_peer_ptrs]
+        self.local_ptr = self._raw_ptr + GUARD_BYTES
+        self.peer_ptrs = [p + GUARD_BYTES for p in self._raw_peers]
+        self.device = torch.device(device)
         self._owner = owner  # keeps the torch tensor alive in the emulated case
         self._ipc = ipc
         self._closed = False
+        for g in self._guard_views():
+            g.fill_(GUARD_PATTERN)
+
+    def _guard_views(self):
+        return (bytes_view(self._raw_ptr, GUARD_BYTES, self.device),
+                bytes_view(self.local_ptr + self.nbytes, GUARD_BYTES, self.device))
+
+    def tensor(self) -> torch.Tensor:
+        """uint8 view of the usable region (without the guard bands)."""
+        return bytes_view(self.local_ptr, self.nbytes, self.device)
+
+    def guards_intact(self) -> bool:
+        """True when both canary bands still hold the pattern (synchronises)."""
+        return all(bool((g == GUARD_PATTERN).all().item()) for g in self._guard_views())
 
     @classmethod
     def create_emulated(cls, world: int, nbytes: int, device: torch.device) -> List["SymmetricRegion"]:
         """P regions on one GPU; every 'peer' address is a local address."""
-        bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
+        bufs = [torch.zeros(nbytes + 2 * GUARD_BYTES, dtype=torch.uint8, device=device) for _ in range(world)]
         ptrs = [b.data_ptr() for b in bufs]
-        return [cls(r, world, nbytes, ptrs[r], ptrs, owner=bufs[r]) for r in range(world)]
+        return [cls(r, world, nbytes, ptrs[r], ptrs, device, owner=bufs[r]) for r in range(world)]
 
     @classmethod
     def create_ipc(cls, nbytes: int, group=None) -> "SymmetricRegion":
@@ -57,7 +80,7 @@ class SymmetricRegion:
         L = _lib.lib()
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         ptr = C.c_void_p()
-        _lib.check(L.gtk_p2p_alloc(int(nbytes), C.byref(ptr)), "gtk_p2p_alloc")
+        _lib.check(L.gtk_p2p_alloc(int(nbytes) + 2 * GUARD_BYTES, C.byref(ptr)), "gtk_p2p_alloc")
         hbytes = int(L.gtk_p2p_handle_bytes())
         hbuf = (C.c_char * hbytes)()
         _lib.check(L.gtk_p2p_export(ptr, hbuf), "gtk_p2p_export")
@@ -73,17 +96,17 @@ class SymmetricRegion:
             _lib.check(L.gtk_p2p_import(src, C.byref(out)), "gtk_p2p_import")
             peers.append(out.value)
         dist.barrier(group=group)
-        return cls(rank, world, nbytes, ptr.value, peers, ipc=True)
+        return cls(rank, world, nbytes, ptr.value, peers, torch.device("cuda", torch.cuda.current_device()), ipc=True)
 
     def close(self) -> None:
         if self._closed or not self._ipc:
             self._closed = True
             return
         L = _lib.lib()
-        for q, p in enumerate(self.peer_ptrs):
+        for q, p in enumerate(self._raw_peers):
             if q != self.rank:
                 L.gtk_p2p_unmap(p)
-        L.gtk_p2p_free(self.local_ptr)
+        L.gtk_p2p_free(self._raw_ptr)
         self._closed = True
 
 
@@ -120,12 +143,6 @@ class ExchangeRank:
                                      int(with_allgather), world, peers), "gtk_k2rank_fill")
         self.desc_host = bytes(host)
         self.desc = torch.frombuffer(bytearray(self.desc_host), dtype=torch.uint8).to(dev)
-
-    # views into the local symmetric region (emulated regions only expose a tensor)
-    def _region_tensor(self) -> torch.Tensor:
-        if self.region._owner is None:
-            raise RuntimeError("no tensor view for an IPC region; use gout_view()")
-        return self.region._owner
 
     def gout_ptr(self, parity: int) -> int:
         return self.region.local_ptr + self.layout[2] + parity * self.kcap * 8
@@ -213,6 +230,16 @@ def launch_allgather(ranks: Sequence[ExchangeRank], desc: torch.Tensor, seg_coun
 
 def region_bytes(kcap: int, with_allgather: bool) -> int:
     return symm_layout(kcap, with_allgather)[4]
+
+
+def bytes_view(ptr: int, n: int, device: torch.device) -> torch.Tensor:
+    """uint8 [n] tensor over raw device memory."""
+
+    class _Holder:
+        __cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (int(ptr), False), "version": 3,
+                                    "strides": None}
+
+    return torch.as_tensor(_Holder(), device=device)
 
 
 def pairs_view(ptr: int, n: int, device: torch.device) -> torch.Tensor:

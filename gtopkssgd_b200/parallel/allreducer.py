@@ -189,6 +189,10 @@ class GroupEngine:
             msg = "group %s: %s (code location %d)" % (self.g.key[:40], STATUS_NAMES.get(status, status), where)
             self.owner.report_failure(msg)
             raise GTopkTimeout(msg)
+        region = getattr(self, "region", None)
+        if region is not None and not region.guards_intact():
+            raise RuntimeError("group %s: a store landed outside the exchange slots (guard band of the "
+                               "peer-visible region was overwritten)" % self.g.key[:40])
 
 
 class AllReducer:

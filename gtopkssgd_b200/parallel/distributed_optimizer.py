@@ -35,7 +35,7 @@ from ..settings import logger
 from . import allreducer as ar
 from . import comm
 from .compression import NoneCompressor
-from .elastic import Membership, PeerLeft
+from .elastic import Membership, PeerLeft, StreamWatchdog
 from .flat_buffer import FlatBuffers
 
 
@@ -80,7 +80,12 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         # changes, so that a captured CUDA graph follows the LR schedule
         self._lr_dev = torch.zeros(1, dtype=torch.float32, device=dev)
         self._lr_host = None
-        self.capturing = False
+        self._capturing = False
+        self._stalled: Optional[str] = None
+        self._watchdog: Optional[StreamWatchdog] = None
+        if self._is_cuda and comm.size() > 1 and settings.WATCHDOG_S >= 0:
+            limit = settings.WATCHDOG_S or (2e-3 * self._allreducer.wait_limit_ms + 30.0)
+            self._watchdog = StreamWatchdog(limit, self._on_stall)
         self._post_clip: Optional[ClipNorm] = None
         self._post_coef: Optional[torch.Tensor] = None
         self._hook_handles = []
@@ -92,6 +97,33 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                       for pg in self.param_groups)
         if not uniform:
             raise ValueError("the fused step needs the same hyper-parameters in every param group")
+
+    # -- watchdog --------------------------------------------------------------
+    @property
+    def capturing(self) -> bool:
+        return self._capturing
+
+    @capturing.setter
+    def capturing(self, value: bool) -> None:
+        """Set around CUDA-graph capture of an iteration; the watchdog thread
+        makes no CUDA call meanwhile."""
+        self._capturing = bool(value)
+        if self._watchdog is not None:
+            (self._watchdog.pause if value else self._watchdog.resume)()
+
+    def _on_stall(self, seconds: float) -> None:
+        msg = "device work of iteration %d still running after %.0f s" % (self._allreducer.train_iter, seconds)
+        self._stalled = msg
+        self._allreducer.report_failure(msg)
+
+    def post_iteration(self) -> None:
+        """Everything of an iteration has been enqueued: hand the watchdog an
+        event behind it."""
+        if self._watchdog is None or self._capturing:
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        self._watchdog.arm(ev)
 
     # -- hooks -----------------------------------------------------------------
     def _register_hooks(self):
@@ -138,6 +170,9 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         iteration is launched.  If a peer has left, the trainer's ``err_handler``
         is told the new world size and GTopkTimeout is raised here, on the host,
         instead of a device-side wait running out later."""
+        if self._stalled is not None and not self.capturing:
+            msg, self._stalled = self._stalled, None
+            raise ar.GTopkTimeout(msg)
         m = self._membership
         if m is None or self.capturing:
             return
@@ -274,6 +309,7 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         a = self._allreducer
         a.train_iter += 1
         a.maybe_print_profiling()
+        self.post_iteration()
         return ret
 
     def check_status(self):
@@ -282,6 +318,9 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         self._allreducer.check_status()
 
     def stop(self):
+        if self._watchdog is not None:
+            self._watchdog.stop()
+            self._watchdog = None
         if self._membership is not None:
             self._membership.leave()
         self._allreducer.stop()

@@ -11,8 +11,9 @@ waits of the exchange itself.
 """
 from __future__ import annotations
 
+import threading
 import time
-from typing import List, Optional
+from typing import Callable, List, Optional
 
 import torch.distributed as dist
 
@@ -94,3 +95,73 @@ class Membership:
         silent = self.stale()
         if silent:
             raise PeerLeft(silent, "stopped sending heartbeats")
+
+
+class StreamWatchdog:
+    """Host thread that watches the device work of the last iteration.
+
+    After an iteration has been enqueued the trainer records an event behind it
+    and calls ``arm(event)``; the thread polls ``event.query()`` and, if the
+    event has not completed ``limit_s`` seconds later, calls ``on_stall(seconds)``
+    once.  Every device-side wait of the exchange is bounded, so the event does
+    complete eventually; the watchdog reports a stream that is stuck for another
+    reason (a peer process stopped inside a library collective, a wedged
+    driver call) while the Python thread sits in a blocking read.
+
+    ``pause()`` / ``resume()`` bracket CUDA-graph capture: a query from another
+    thread during a global-mode capture would invalidate the capture, so while
+    paused the thread makes no CUDA call at all (``pause`` returns only after a
+    query in flight has finished).
+    """
+
+    def __init__(self, limit_s: float, on_stall: Callable[[float], None], poll_s: float = 0.25):
+        self.limit_s, self.poll_s, self.on_stall = float(limit_s), float(poll_s), on_stall
+        self._lock = threading.Lock()
+        self._event = None
+        self._armed_at = 0.0
+        self._paused = False
+        self._stop = threading.Event()
+        self.stalls = 0
+        self._thread = threading.Thread(target=self._run, name="gtopk-watchdog", daemon=True)
+        self._thread.start()
+
+    def arm(self, event) -> None:
+        with self._lock:
+            if not self._paused:
+                self._event, self._armed_at = event, time.monotonic()
+
+    def disarm(self) -> None:
+        with self._lock:
+            self._event = None
+
+    def pause(self) -> None:
+        with self._lock:
+            self._paused, self._event = True, None
+
+    def resume(self) -> None:
+        with self._lock:
+            self._paused = False
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._thread.join(timeout=2.0)
+
+    def _run(self) -> None:
+        while not self._stop.wait(self.poll_s):
+            fire = None
+            with self._lock:
+                if self._paused or self._event is None:
+                    continue
+                if self._event.query():
+                    self._event = None
+                    continue
+                waited = time.monotonic() - self._armed_at
+                if waited > self.limit_s:
+                    self._event = None
+                    self.stalls += 1
+                    fire = waited
+            if fire is not None:
+                try:
+                    self.on_stall(fire)
+                except Exception:  # a reporting problem must not end the thread
+                    pass

@@ -31,8 +31,16 @@ PIN_DENSITY = _env_flag("PIN_DENSITY", False)
 # Merge threshold in elements; a group closes once it holds this many
 # (allreducer.py:26: 640 Mi elements, i.e. the whole model is one group).
 THRESHOLD = int(os.environ.get("GTOPK_THRESHOLD", str(640 * 1024 * 1024)))
+# NVTX ranges around every phase of the gradient path (select, exchange,
+# update) and around each training step, for timeline tools.
+NVTX = _env_flag("NVTX", False)
 # Limit of every device-side wait, in milliseconds.
 WAIT_LIMIT_MS = float(os.environ.get("GTOPK_WAIT_LIMIT_MS", "20000"))
+
+# Host watchdog on the device work of an iteration, multi-GPU runs only: seconds
+# after which a still-running iteration is reported (0 = twice the device wait
+# limit plus 30 s; negative = no watchdog).
+WATCHDOG_S = float(os.environ.get("GTOPK_WATCHDOG_S", "0"))
 
 PREFIX = ("compression" if SPARSE else "baseline") + ("-gwarmup" if WARMUP else "")
 PREFIX += "-dc%d" % DELAY_COMM + "-model-ijcai2019"

@@ -563,6 +563,11 @@ class DLTrainer:
         trainer's ``use_cuda_graph``) the whole iteration is captured once as a
         CUDA graph and replayed.  Returns the carried hidden state for the LSTM
         model, else None."""
+        from ..utils.timing import nvtx_range
+        with nvtx_range("gtopk/train_step"):
+            return self._train_step(data, hidden, clip_norm, cuda_graph)
+
+    def _train_step(self, data, hidden, clip_norm, cuda_graph):
         use_graph = self.use_cuda_graph if cuda_graph is None else cuda_graph
         if not (use_graph and self.is_cuda and self.dnn != "lstman4"):
             self.optimizer.zero_grad()

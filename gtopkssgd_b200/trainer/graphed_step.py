@@ -129,6 +129,8 @@ class GraphedStep:
         if hasattr(opt, "pre_iteration"):
             opt.pre_iteration()  # a replay runs no Python of the iteration, so look at the membership here
         g.replay()
+        if hasattr(opt, "post_iteration"):
+            opt.post_iteration()
         _native.add_launches(st["native_launches"])
         a = getattr(opt, "_allreducer", None)
         if a is not None:

@@ -8,6 +8,7 @@ around device synchronisations.
 """
 from __future__ import annotations
 
+import contextlib
 import statistics
 import subprocess
 import threading
@@ -15,6 +16,28 @@ from collections import defaultdict
 from typing import Dict, List, Optional
 
 import torch
+
+from .. import settings
+
+
+def nvtx_push(name: str) -> None:
+    if settings.NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+
+
+def nvtx_pop() -> None:
+    if settings.NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_pop()
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """NVTX range when ``settings.NVTX`` is on; nothing otherwise."""
+    nvtx_push(name)
+    try:
+        yield
+    finally:
+        nvtx_pop()
 
 
 class CudaTimer:
@@ -76,12 +99,14 @@ class PhaseTimers:
         return d[phase]
 
     def start(self, group: str, phase: str) -> None:
+        nvtx_push("gtopk/" + phase)
         if self.enabled:
             self.timer(group, phase).start()
 
     def stop(self, group: str, phase: str) -> None:
         if self.enabled:
             self.timer(group, phase).stop()
+        nvtx_pop()
 
     def add_host(self, group: str, phase: str, seconds: float) -> None:
         if self.enabled:

@@ -412,3 +412,56 @@ def test_gtopk_cli_smoke_an4_synthetic(tmp_path, monkeypatch):
                         "--max-epochs", "1", "--max-iters", "1"])
     logdir = tmp_path / "logs"
     assert any("lstman4-n1-bs2-lr0.0003-ns1-sg2.50-ds0.001" in dp for dp, _, _ in os.walk(logdir))
+
+
+def test_nvtx_ranges_follow_the_switch(monkeypatch):
+    """With settings.NVTX on, every timed phase and every train step is wrapped
+    in a balanced NVTX range; with it off nothing is pushed."""
+    from gtopkssgd_b200.utils import timing
+    events = []
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: events.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: events.append(("pop", None)))
+    t = timing.PhaseTimers(enabled=False)
+    t.start("g", "compression")
+    t.stop("g", "compression")
+    assert events == []
+    monkeypatch.setattr(settings, "NVTX", True)
+    t.start("g", "compression")
+    with timing.nvtx_range("gtopk/train_step"):
+        pass
+    t.stop("g", "compression")
+    assert events == [("push", "gtopk/compression"), ("push", "gtopk/train_step"), ("pop", None), ("pop", None)]
+
+
+def test_stream_watchdog_reports_a_stuck_iteration_once():
+    import time
+    from gtopkssgd_b200.parallel.elastic import StreamWatchdog
+
+    class FakeEvent:
+        def __init__(self, done_after=None):
+            self.t0, self.done_after, self.queries = time.monotonic(), done_after, 0
+
+        def query(self):
+            self.queries += 1
+            return self.done_after is not None and time.monotonic() - self.t0 >= self.done_after
+
+    stalls = []
+    w = StreamWatchdog(0.2, stalls.append, poll_s=0.02)
+    try:
+        w.arm(FakeEvent(done_after=0.05))          # completes in time
+        time.sleep(0.4)
+        assert stalls == []
+        stuck = FakeEvent()
+        w.arm(stuck)                               # never completes
+        time.sleep(0.5)
+        assert len(stalls) == 1 and stalls[0] > 0.2 and w.stalls == 1
+        w.pause()                                  # graph capture: no query while paused, and arming is dropped
+        n = stuck.queries
+        w.arm(stuck)
+        w.pause()
+        time.sleep(0.1)
+        assert stuck.queries == n and len(stalls) == 1
+        w.resume()
+    finally:
+        w.stop()

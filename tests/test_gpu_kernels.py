@@ -225,7 +225,7 @@ def _read_gout(rank, parity):
     from gtopkssgd_b200.ops.select import pairs_to_tensors
     n = int(rank.n_global.item())
     off = rank.layout[2] + parity * rank.kcap * 8
-    raw = rank.region._owner[off:off + n * 8].view(torch.int32).view(n, 2)
+    raw = rank.region.tensor()[off:off + n * 8].view(torch.int32).view(n, 2)
     return pairs_to_tensors(raw, n)
 
 
@@ -255,6 +255,21 @@ def test_k2_gtopk_exchange_emulated(P, d, k, nctas):
             for j in ref:
                 assert got[j] == pytest.approx(ref[j], rel=1e-5, abs=1e-6)
             assert torch.allclose(r.resid.cpu(), res_ref[r.rank], rtol=1e-5, atol=1e-6)
+            assert r.region.guards_intact(), "a store landed outside the slots of rank %d" % r.rank
+
+
+def test_region_guard_bands_detect_a_stray_write():
+    """The canary bands around a peer-visible region are checked by reading
+    them back; an ordinary torch write into the band (inside the same
+    allocation) must be noticed."""
+    from gtopkssgd_b200.ops import exchange as ex
+    regions = ex.SymmetricRegion.create_emulated(2, ex.region_bytes(64, True), DEV)
+    assert all(r.guards_intact() for r in regions)
+    assert regions[0].tensor().numel() == regions[0].nbytes
+    regions[0].tensor().fill_(7)              # the whole usable region may be written
+    assert regions[0].guards_intact()
+    regions[1]._owner[ex.GUARD_BYTES + regions[1].nbytes + 3] = 0   # first band byte range after the region
+    assert not regions[1].guards_intact() and regions[0].guards_intact()
 
 
 @pytest.mark.parametrize("mode", ["topk", "topk2"])
@@ -282,7 +297,7 @@ def test_k2t_allgather_emulated(P, mode):
             assert r.last_parity() == epoch & 1
             base = r.layout[1] + r.last_parity() * ex.MAX_PEERS * k * 8
             for q in range(P):
-                raw = r.region._owner[base + q * k * 8: base + (q + 1) * k * 8].view(torch.int32).view(k, 2)
+                raw = r.region.tensor()[base + q * k * 8: base + (q + 1) * k * 8].view(torch.int32).view(k, 2)
                 qi, qv = pairs_to_tensors(raw, k)
                 assert set(qi.cpu().tolist()) == set(local[q][0].tolist())
         if mode == "topk2":
