@@ -84,7 +84,8 @@ class GroupEngine:
         fb = owner.flat
         self.grad = fb.group_slice(fb.grad, g)
         self.resid = fb.group_slice(fb.residual, g) if fb.residual is not None else None
-        self.numel = g.numel
+        self.numel = g.numel                # span in the flat buffers: what the kernels run over
+        self.param_numel = g.param_numel    # number of parameters: what the density applies to
         self.last_k = 0
         self.result: Optional[SparseResult] = None
         self.dense_ready = False
@@ -94,7 +95,7 @@ class GroupEngine:
         if mode == "none":
             return
         dens = max(owner.densities()) if owner.densities() else owner._density
-        self.max_k = oracle.num_selected(self.numel, dens)
+        self.max_k = oracle.num_selected(self.param_numel, dens)
         self.selector = TopkSelector(self.numel, self.max_k, dev, limit_ms=owner.wait_limit_ms)
         self.rank_ctx = None
         world = owner.size()
@@ -117,7 +118,7 @@ class GroupEngine:
         """Enqueue select + exchange for this group on the current stream."""
         o = self.owner
         world, mode = o.size(), o.mode
-        k = oracle.num_selected(self.numel, density)
+        k = oracle.num_selected(self.param_numel, density)
         k = min(k, self.max_k)
         self.last_k = k
         t = o.timers
@@ -233,7 +234,7 @@ class AllReducer:
         self._merged_parameters = {g.key: self.flat.group_slice(self.flat.grad, g) for g in self.flat.groups}
         self._merged_parameter_offsets = {g.key: g.offsets for g in self.flat.groups}
         self._sizes = [self._named_parameters[k].numel() for k in self._sequential_keys][::-1]
-        logger.info("groups: %d, sizes: %s", len(self._groups), [g.numel for g in self.flat.groups])
+        logger.info("groups: %d, sizes: %s", len(self._groups), [g.param_numel for g in self.flat.groups])
         # dynamic densities (allreducer.py:226-230): epoch 0 -> 0.004, then --density
         self._dynamic_densities = None if settings.PIN_DENSITY else [0.004, self._density]
         if self._dynamic_densities is not None:
@@ -333,9 +334,9 @@ class AllReducer:
             m = self.timers.means(e.g.key)
             row = [m[p] for p in PhaseTimers.PHASES]
             tot += np.array(row)
-            total_sz += e.numel
+            total_sz += e.param_numel
             k = e.g.key
-            logger.info("[rank:%d]%s[%d]: %f,%f,%f,%f,%f,%f,%f", self.rank(), k[0:3] + "..." + k[-3:], e.numel, *row)
+            logger.info("[rank:%d]%s[%d]: %f,%f,%f,%f,%f,%f,%f", self.rank(), k[0:3] + "..." + k[-3:], e.param_numel, *row)
         logger.info("[rank:%d]%s[%d]: %f,%f,%f,%f,%f,%f,%f", self.rank(), "total", total_sz, *tot.tolist())
 
     def _profiling_before(self, eng: GroupEngine):
@@ -356,7 +357,7 @@ class AllReducer:
                 n = int(res.counts[s])
                 idx, val = pairs_to_tensors(live[s * res.seg_stride:(s + 1) * res.seg_stride], n)
                 sparse.index_add_(0, idx.to(sparse.device), val.to(sparse.device) * res.scale)
-            k = oracle.num_selected(eng.numel, self.get_current_density())
+            k = oracle.num_selected(eng.param_numel, self.get_current_density())
             perm = torch.randperm(dense_ref.numel(), device=dense_ref.device)[:k]
             randk = torch.zeros_like(dense_ref)
             randk[perm] = dense_ref[perm]

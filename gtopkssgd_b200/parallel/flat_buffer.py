@@ -19,7 +19,11 @@ from typing import Dict, Iterable, List, Sequence, Tuple
 
 import torch
 
-ALIGN = 64  # elements; every group starts on a 256-byte boundary
+ALIGN = 64      # elements; every group starts on a 256-byte boundary
+SLOT_ALIGN = 4  # elements; every parameter starts on a 16-byte boundary.  Library kernels (cuDNN, cuBLAS)
+                # pick their vectorised and TMA-fed variants only for 16-byte aligned operands, and a
+                # channels-last convolution faulted with "misaligned address" on an 8-byte aligned weight view
+                # (VGG-16, whose 10-element classifier bias shifted every later parameter).
 
 
 @dataclass
@@ -37,9 +41,10 @@ class MergedGroup:
     index: int
     names: List[str]
     start: int       # element offset of the group inside the flat buffers
-    numel: int       # elements that belong to parameters
+    numel: int       # span of the group in the flat buffers (parameters + alignment gaps, which stay zero)
     offsets: List[int] = field(default_factory=list)   # per-parameter offsets inside the group
     key: str = ""
+    param_numel: int = 0   # elements that belong to parameters: the d that the density applies to
 
 
 def generate_groups(names_in_order: Sequence[str], sizes: Dict[str, int], threshold: int) -> Tuple[List[List[str]], Dict[str, int]]:
@@ -87,14 +92,18 @@ class FlatBuffers:
         for gi, gnames in enumerate(group_names):
             start = cursor
             offs = []
+            end = cursor
             for n in gnames:
                 offs.append(cursor - start)
                 self.slots[n] = ParamSlot(n, by_name[n], gi, cursor, sizes[n])
-                cursor += sizes[n]
-            self.groups.append(MergedGroup(gi, list(gnames), start, cursor - start, offs, ":".join(gnames)))
+                end = cursor + sizes[n]
+                cursor = (end + SLOT_ALIGN - 1) // SLOT_ALIGN * SLOT_ALIGN
+            self.groups.append(MergedGroup(gi, list(gnames), start, end - start, offs, ":".join(gnames),
+                                           sum(sizes[n] for n in gnames)))
             cursor = (cursor + ALIGN - 1) // ALIGN * ALIGN
         self.total = cursor
         self.numel = sum(g.numel for g in self.groups)
+        self.param_numel = sum(g.param_numel for g in self.groups)
         self.param = torch.zeros(self.total, dtype=dtype, device=dev)
         self.grad = torch.zeros(self.total, dtype=dtype, device=dev)
         self.momentum = torch.zeros(self.total, dtype=dtype, device=dev)

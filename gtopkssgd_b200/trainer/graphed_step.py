@@ -62,7 +62,7 @@ class GraphedStep:
         a = getattr(opt, "_allreducer", None)
         if a is not None and a.mode != "none":
             from ..ops.oracle import num_selected
-            ks = tuple(min(num_selected(e.numel, a.get_current_density()), e.max_k) for e in a.engines)
+            ks = tuple(min(num_selected(e.param_numel, a.get_current_density()), e.max_k) for e in a.engines)
         return (tuple(x.shape), tuple(y.shape), ks, bool(getattr(opt, "_materialized", False)))
 
     def _capture(self, sig, x, y, hidden):

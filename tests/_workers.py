@@ -42,7 +42,7 @@ def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="
     crit = torch.nn.CrossEntropyLoss()
     fb = dopt._flat
     trace = {"p0": fb.param.detach().cpu().clone(), "grads": [], "params": [], "resid": [],
-             "groups": [(g.start, g.numel) for g in fb.groups]}
+             "groups": [(g.start, g.numel, g.param_numel) for g in fb.groups]}
     for it in range(iters):
         x, y = _make_batch(rank, it, 8)
         dopt.zero_grad()
@@ -86,7 +86,7 @@ def graphed_step_worker(rank, world, iters, compressor):
     fb = dopt._flat
     step = GraphedStep(t, warmup=3)
     trace = {"p0": fb.param.detach().cpu().clone(), "grads": [], "params": [], "resid": [], "lrs": [],
-             "numel": fb.numel}
+             "numel": fb.numel, "groups": [(g.start, g.numel, g.param_numel) for g in fb.groups]}
     for it in range(iters):
         x, y = _make_batch(rank, it, 8)
         lr = 0.1 if it < 4 else 0.05

@@ -19,15 +19,18 @@ def replay_and_check(traces, density, compressor, rtol=1e-5, atol=1e-6):
     later gradient.)"""
     world = len(traces)
     total = traces[0]["p0"].numel()
-    groups = traces[0].get("groups") or [(0, traces[0]["numel"])]
+    # (start, span in the flat buffer, parameter count): k follows the parameter count, the alignment
+    # gaps inside a span hold zeros and never win
+    groups = [tuple(g) if len(g) == 3 else (g[0], g[1], g[1])
+              for g in (traces[0].get("groups") or [(0, traces[0]["numel"])])]
     res = [torch.zeros(total) for _ in range(world)]
     bufs = [torch.zeros(total) for _ in range(world)]
     params = [t["p0"].clone() for t in traces]
     for it in range(len(traces[0]["grads"])):
         dense = torch.zeros(total)
-        for start, numel in groups:
+        for start, numel, nparam in groups:
             sl = slice(start, start + numel)
-            k = oracle.num_selected(numel, density)
+            k = oracle.num_selected(nparam, density)
             grads = [t["grads"][it][sl] for t in traces]
             rs = [r[sl] for r in res]  # views: updated in place
             if compressor == "gtopk":
@@ -50,7 +53,7 @@ def replay_and_check(traces, density, compressor, rtol=1e-5, atol=1e-6):
             lr = traces[r]["lrs"][it] if "lrs" in traces[r] else 0.1
             oracle.sgd_step(params[r], bufs[r], dense, lr, 0.9, 0.0, 1e-4, False, first_step=(it == 0))
             got = traces[r]["params"][it]
-            for start, numel in groups:  # padding between groups is not compared
+            for start, numel, _ in groups:  # padding between groups is not compared
                 sl = slice(start, start + numel)
                 assert torch.allclose(got[sl], params[r][sl], rtol=rtol, atol=atol), \
                     (it, r, start, float((got[sl] - params[r][sl]).abs().max()))

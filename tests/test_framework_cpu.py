@@ -54,7 +54,8 @@ def test_flat_buffers_keep_views_and_values():
     net, _ = create_net(10, "resnet20")
     before = {n: p.detach().clone() for n, p in net.named_parameters()}
     fb = FlatBuffers(net.named_parameters(), 100000)
-    assert len(fb.groups) == 3 and fb.numel == 269722
+    assert len(fb.groups) == 3 and fb.param_numel == 269722
+    assert all(s.offset % 4 == 0 for s in fb.slots.values())  # every parameter view is 16-byte aligned
     for n, p in net.named_parameters():
         assert torch.equal(p, before[n])
         s = fb.slots[n]
