@@ -29,7 +29,7 @@ writer = None
 
 
 def ssgd_dense(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, nwpernode, pretrain,
-               num_steps=1, max_iters=None, threshold=None, cuda_graph=None):
+               num_steps=1, max_iters=None, threshold=None, cuda_graph=None, prefetch=None):
     use_cuda = torch.cuda.is_available()
     rank = comm.rank()
     if use_cuda:
@@ -40,6 +40,8 @@ def ssgd_dense(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, 
                         ngpus=1 if use_cuda else 0, data_dir=data_dir, dataset=dataset, dnn=dnn, lr=lr,
                         nworkers=nworkers, prefix="allreduce", pretrain=pretrain, num_steps=num_steps,
                         tb_writer=writer, cuda_graph=cuda_graph)
+    if prefetch is not None:
+        trainer.prefetch_batches = bool(prefetch)
     trainer.set_train_epoch(int(comm.broadcast_object(trainer.get_train_epoch())))
     trainer.set_train_iter(int(comm.broadcast_object(trainer.get_train_iter())))
     comm.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
@@ -105,6 +107,7 @@ def main(argv=None):
     p.add_argument("--max-iters", type=int, default=None)
     p.add_argument("--threshold", type=int, default=None)
     p.add_argument("--cuda-graph", action="store_true")
+    p.add_argument("--prefetch", action="store_true")
     args = p.parse_args(argv)
     comm.init()
     if comm.size() > 1:
@@ -125,7 +128,7 @@ def main(argv=None):
     try:
         ssgd_dense(args.dnn, args.dataset, args.data_dir, args.nworkers, args.lr, args.batch_size, args.nsteps_update,
                    args.max_epochs, args.nwpernode, args.pretrain, args.num_steps, args.max_iters, args.threshold,
-                   args.cuda_graph or None)
+                   args.cuda_graph or None, args.prefetch or None)
     finally:
         if writer is not None:
             writer.close()

@@ -58,6 +58,14 @@ class _CTC(nn.Module):
                                             label_lens.to(torch.long), blank=0, reduction="sum", zero_infinity=True)
 
 
+class PrefetchedBatch:
+    """A batch whose device copy is in flight on the copy stream (see ``DLTrainer.prefetch``)."""
+    __slots__ = ("tensors", "event")
+
+    def __init__(self, tensors, event):
+        self.tensors, self.event = tensors, event
+
+
 class DLTrainer:
     def __init__(self, rank, size, master="gpu10", dist=True, ngpus=1, batch_size=32, is_weak_scaling=True,
                  data_dir="./data", dataset="cifar10", dnn="resnet20", lr=0.04, nworkers=1, prefix=None,
@@ -78,6 +86,9 @@ class DLTrainer:
         self.train_sampler = None
         self.ext = None
         self.use_cuda_graph = os.environ.get("GTOPK_CUDA_GRAPH", "0") == "1" if cuda_graph is None else bool(cuda_graph)
+        self._copy_stream = None
+        self.prefetch_batches = os.environ.get("GTOPK_PREFETCH", "0") == "1"
+        self._inflight = None
         self._graphed = None
         if not isinstance(dnn, str):
             self.net, self.dnn = dnn, dnn.name
@@ -394,11 +405,21 @@ class DLTrainer:
             self.testloader = torch.utils.data.DataLoader(self.testset, batch_size=self.batch_size, shuffle=False,
                                                           num_workers=0 if self.synthetic else 1)
         self.data_iterator = None
+        self._inflight = None
         n = self.get_num_of_training_samples()
         self.num_batches_per_epoch = (n + self.batch_size * nworkers - 1) // (self.batch_size * nworkers)
 
     def data_iter(self):
-        """Endless batch iterator; short last batches are skipped."""
+        """Endless batch iterator; short last batches are skipped.  With
+        ``prefetch_batches`` on a GPU the batch after the returned one is
+        already on its way to the device (see ``prefetch``)."""
+        if not (self.prefetch_batches and self.is_cuda):
+            return self._next_host_batch()
+        cur = self._inflight if self._inflight is not None else self.prefetch(self._next_host_batch())
+        self._inflight = self.prefetch(self._next_host_batch())
+        return cur
+
+    def _next_host_batch(self):
         while True:
             if self.data_iterator is None:
                 self.data_iterator = iter(self.trainloader)
@@ -494,7 +515,31 @@ class DLTrainer:
         if self.train_sampler is not None and self.nworkers > 1 and hasattr(self.train_sampler, "set_epoch"):
             self.train_sampler.set_epoch(self.train_epoch)
 
+    def prefetch(self, data):
+        """Start the host-to-device copy of a batch (pinned memory makes it
+        asynchronous) on the trainer's copy stream and return a handle that
+        ``train`` / ``train_step`` accept as ``data``.  The copy runs while the
+        compute stream works on the previous iteration; the consumer waits for
+        it on the device (a stream wait, no host synchronisation).  Without a
+        GPU the batch is returned unchanged."""
+        if not self.is_cuda or isinstance(data, PrefetchedBatch):
+            return data
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        with torch.cuda.stream(self._copy_stream):
+            tensors = self._to_device(data)
+            ev = torch.cuda.Event()
+            ev.record()
+        return PrefetchedBatch(tensors, ev)
+
     def _to_device(self, data):
+        if isinstance(data, PrefetchedBatch):
+            cur = torch.cuda.current_stream(self.device)
+            cur.wait_event(data.event)
+            for t in data.tensors:
+                if torch.is_tensor(t) and t.is_cuda:
+                    t.record_stream(cur)  # allocated on the copy stream, consumed here
+            return data.tensors
         if self.dataset == "an4":
             inputs, labels_cpu, pct, target_sizes = data
             input_sizes = pct.mul(int(inputs.size(3))).int()

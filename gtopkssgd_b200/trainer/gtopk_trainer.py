@@ -51,7 +51,8 @@ def _dump_profiling_norms(optimizer, rank, epoch):
 
 def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, compression=False,
                 compressor="topk", nwpernode=1, sigma_scale=2.5, pretrain=None, density=0.01, prefix=None,
-                max_iters=None, threshold=None, save_checkpoints=None, check_every=50, cuda_graph=None):
+                max_iters=None, threshold=None, save_checkpoints=None, check_every=50, cuda_graph=None,
+                prefetch=None):
     use_cuda = torch.cuda.is_available()
     rank = dopt.rank()
     if use_cuda:
@@ -63,6 +64,8 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
                         ngpus=1 if use_cuda else 0, data_dir=data_dir, dataset=dataset, dnn=dnn, lr=lr,
                         nworkers=nworkers, prefix=prefix, pretrain=pretrain, tb_writer=writer,
                         save_checkpoints=save_checkpoints, cuda_graph=cuda_graph)
+    if prefetch is not None:
+        trainer.prefetch_batches = bool(prefetch)
     trainer.set_train_epoch(comm.broadcast_object(trainer.get_train_epoch()))
     trainer.set_train_iter(comm.broadcast_object(trainer.get_train_iter()))
 
@@ -150,6 +153,8 @@ def build_parser():
     p.add_argument("--save-checkpoints", action="store_true", help="Write a checkpoint at every epoch end")
     p.add_argument("--cuda-graph", action="store_true",
                    help="Capture the whole iteration as a CUDA graph (pays off for launch-bound models)")
+    p.add_argument("--prefetch", action="store_true",
+                   help="Copy the next batch to the device on a side stream while the current iteration runs")
     p.set_defaults(compression=False)
     return p
 
@@ -187,7 +192,7 @@ def main(argv=None):
                     args.nsteps_update, args.max_epochs, args.compression, args.compressor, args.nwpernode,
                     args.sigma_scale, args.pretrain, args.density, prefix, max_iters=args.max_iters,
                     threshold=args.threshold, save_checkpoints=args.save_checkpoints or None,
-                    cuda_graph=args.cuda_graph or None)
+                    cuda_graph=args.cuda_graph or None, prefetch=args.prefetch or None)
     finally:
         if writer is not None:
             writer.close()

@@ -80,3 +80,48 @@ def test_two_gpu_cuda_graph_step_matches_oracle(compressor, graphs):
 def test_graft_smoke():
     import __graft_entry__ as g
     g.smoke()
+
+
+def test_prefetched_batches_train_like_host_batches():
+    """DLTrainer.prefetch copies a pinned batch on a side stream.  The consumer
+    sees exactly the host data (also while the compute stream is busy), and
+    ``train_step`` takes the handle in the eager and the CUDA-graph path: the
+    first step, which depends only on the initial weights and the batch, gives
+    the same loss as with the host batch."""
+    import torch
+    from gtopkssgd_b200.trainer.dl_trainer import DLTrainer, PrefetchedBatch
+
+    def trainer(graph):
+        torch.manual_seed(0)
+        return DLTrainer(0, 1, dist=False, ngpus=1, batch_size=8, data_dir="synthetic", dataset="cifar10",
+                         dnn="resnet20", lr=0.1, nworkers=1, device=torch.device("cuda", 0), synthetic_train_size=64,
+                         cuda_graph=graph)
+
+    g = torch.Generator().manual_seed(1)
+    batches = [(torch.randn(8, 3, 32, 32, generator=g).pin_memory(),
+                torch.randint(0, 10, (8,), generator=g).pin_memory()) for _ in range(6)]
+    t = trainer(False)
+    busy = torch.randn(4096, 4096, device="cuda")
+    for b in batches * 3:
+        h = t.prefetch(b)
+        assert isinstance(h, PrefetchedBatch) and t.prefetch(h) is h
+        busy = busy @ busy * 1e-4          # keeps the compute stream occupied while the copy runs
+        x, y, _, _ = t._to_device(h)
+        assert torch.equal(x.cpu(), b[0]) and torch.equal(y.cpu(), b[1])
+
+    for graph in (False, True):
+        first = {}
+        for prefetch in (False, True):
+            t = trainer(graph)
+            nxt, losses = None, []
+            for i, b in enumerate(batches):
+                if prefetch:
+                    cur = nxt if nxt is not None else t.prefetch(b)
+                    nxt = t.prefetch(batches[i + 1]) if i + 1 < len(batches) else None
+                else:
+                    cur = b
+                t.train_step(data=cur)
+                losses.append(t.loss)
+            assert all(l == l and l < 1e3 for l in losses)
+            first[prefetch] = losses[0]
+        assert abs(first[False] - first[True]) < 1e-4, first
