@@ -99,7 +99,10 @@ class GroupEngine:
         self.selector = TopkSelector(self.numel, self.max_k, dev, limit_ms=owner.wait_limit_ms)
         self.rank_ctx = None
         world = owner.size()
-        if world > 1 and self.is_cuda:
+        # CUDA ranks that cannot reach each other's memory (several hosts, no peer access) stage their
+        # sets through the host and gloo, as CPU ranks do
+        self.staged = world > 1 and self.is_cuda and comm.sparse_transport() == "staged"
+        if world > 1 and self.is_cuda and not self.staged:
             with_ag = mode in ("topk", "topk2")
             nbytes = ex.region_bytes(self.max_k, with_ag)
             self.region = ex.SymmetricRegion.create_ipc(nbytes, group=comm.cpu_group())
@@ -128,7 +131,7 @@ class GroupEngine:
         t.start(self.g.key, "allreduce")
         if world == 1:
             self.result = SparseResult(self.selector.sel, self.selector.n_sel_tensor, 1, self.max_k, False, 1.0)
-        elif self.is_cuda:
+        elif self.is_cuda and not self.staged:
             rc = self.rank_ctx
             if mode == "gtopk":
                 ex.launch_gtopk([rc], rc.desc, o.rank(), world, k, limit_ms=o.wait_limit_ms)
@@ -148,29 +151,32 @@ class GroupEngine:
         t.stop(self.g.key, "allreduce")
 
     def _reduce_host(self, k: int, world: int, mode: str) -> None:
-        """CPU tensors: the gloo fallback (also the multi-process oracle)."""
+        """CPU tensors, or CUDA tensors in staged transport: the gloo fallback
+        (also the multi-process oracle).  Synchronises the current stream."""
         o = self.owner
         idx, val = self.selector.pairs()
+        grp = comm.cpu_group()
+        dev = self.resid.device
         try:
             if mode == "gtopk":
-                gi, gv = fallback.gtopk_allreduce(idx, val, k, timeout_s=o.wait_limit_ms / 1e3)
-                oracle.put_back(self.resid, (idx, val), gi)
+                gi, gv = fallback.gtopk_allreduce(idx, val, k, group=grp, timeout_s=o.wait_limit_ms / 1e3)
+                oracle.put_back(self.resid, (idx, val), gi.to(dev))
                 n = tensors_to_pairs(gi, gv, self.host_pairs)
                 self.host_counts[0] = n
                 self.result = SparseResult(self.host_pairs, self.host_counts, 1, self.host_pairs.shape[0], False,
                                            1.0 / world)
             elif mode == "topk":
-                ai, av = fallback.topk_allgather(idx, val)
+                ai, av = fallback.topk_allgather(idx, val, group=grp)
                 n = tensors_to_pairs(ai, av, self.host_pairs)
                 self.host_counts[0] = n
                 self.result = SparseResult(self.host_pairs, self.host_counts, 1, self.host_pairs.shape[0], True,
                                            1.0 / world)
             else:  # topk2
-                ai, av = fallback.topk_allgather(idx, val)
+                ai, av = fallback.topk_allgather(idx, val, group=grp)
                 kk = idx.numel()
                 sets = [(ai[q * kk:(q + 1) * kk], av[q * kk:(q + 1) * kk]) for q in range(world)]
                 gi, gv = oracle.topk2_reselect(sets, k)
-                oracle.put_back(self.resid, (idx, val), gi)
+                oracle.put_back(self.resid, (idx, val), gi.to(dev))
                 n = tensors_to_pairs(gi, gv, self.host_pairs)
                 self.host_counts[0] = n
                 self.result = SparseResult(self.host_pairs, self.host_counts, 1, self.host_pairs.shape[0], False,

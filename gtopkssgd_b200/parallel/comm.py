@@ -57,11 +57,60 @@ def cpu_group():
     return _cpu_group
 
 
+def choose_transport(requested: str, hosts, peer_ok) -> str:
+    """'p2p' or 'staged' for a CUDA world.  ``hosts``: host name of every rank;
+    ``peer_ok``: per rank, whether it can map every other rank's GPU.  'auto'
+    takes p2p only when one host holds all ranks and every rank has peer
+    access; an explicit 'p2p' that cannot work is an error."""
+    possible = len(set(hosts)) == 1 and all(peer_ok)
+    if requested == "staged":
+        return "staged"
+    if requested == "p2p":
+        if not possible:
+            raise RuntimeError("GTOPK_TRANSPORT=p2p needs all ranks on one host with GPU peer access "
+                               "(hosts: %s, peer access: %s)" % (sorted(set(hosts)), list(peer_ok)))
+        return "p2p"
+    if requested != "auto":
+        raise ValueError("GTOPK_TRANSPORT must be auto, p2p or staged (got %r)" % requested)
+    return "p2p" if possible else "staged"
+
+
+_transport = None
+
+
+def sparse_transport() -> str:
+    """The transport of the sparse exchange for this CUDA world (decided once,
+    collectively: every rank gets the same answer)."""
+    global _transport
+    if _transport is not None:
+        return _transport
+    import socket
+    from .. import settings
+    world = size()
+    if world == 1:
+        return "p2p"
+    me = torch.cuda.current_device()
+    mine = (socket.gethostname(), me)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine, group=cpu_group())
+    hosts = [h for h, _ in everyone]
+    ok = True
+    if len(set(hosts)) == 1:
+        for _, other in everyone:
+            if other != me and not torch.cuda.can_device_access_peer(me, other):
+                ok = False
+    oks = [None] * world
+    dist.all_gather_object(oks, ok, group=cpu_group())
+    _transport = choose_transport(settings.TRANSPORT, hosts, oks)
+    return _transport
+
+
 def shutdown() -> None:
-    global _cpu_group
+    global _cpu_group, _transport
     if dist.is_initialized():
         dist.destroy_process_group()
     _cpu_group = None
+    _transport = None
 
 
 def rank() -> int:

@@ -37,6 +37,10 @@ NVTX = _env_flag("NVTX", False)
 # Limit of every device-side wait, in milliseconds.
 WAIT_LIMIT_MS = float(os.environ.get("GTOPK_WAIT_LIMIT_MS", "20000"))
 
+# How CUDA ranks exchange their sparse sets: "p2p" = peer stores over NVLink inside the exchange
+# kernels (all ranks on one host with peer access), "staged" = device -> host -> gloo -> device (ranks on
+# several hosts, or no peer access), "auto" = p2p where possible.
+TRANSPORT = os.environ.get("GTOPK_TRANSPORT", "auto").lower()
 # Host watchdog on the device work of an iteration, multi-GPU runs only: seconds
 # after which a still-running iteration is reported (0 = twice the device wait
 # limit plus 30 s; negative = no watchdog).

@@ -102,7 +102,11 @@ class GraphedStep:
         capturing those needs the process group's asynchronous error handling
         switched off before it is created, so that case stays eager."""
         a = getattr(self.t.optimizer, "_allreducer", None)
-        return not (a is not None and a.mode == "none" and a.size() > 1)
+        if a is None:
+            return True
+        if any(getattr(e, "staged", False) for e in a.engines):
+            return False  # the staged transport reads the selection back on the host every iteration
+        return not (a.mode == "none" and a.size() > 1)
 
     def run(self, x, y, hidden=None):
         """x, y: this iteration's batch on the device.  Returns (loss, acc, hidden)."""

@@ -24,6 +24,7 @@ def resnet20_gtopk_worker(rank, world, iters, density, compressor, device_kind="
     from gtopkssgd_b200.parallel.compression import compressors
     from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
     settings.PIN_DENSITY = True
+    settings.TRANSPORT = os.environ.get("GTOPK_TRANSPORT", settings.TRANSPORT)
     settings.logger.setLevel("WARNING")
     torch.set_num_threads(1)
     dev = torch.device("cpu")

@@ -466,3 +466,16 @@ def test_stream_watchdog_reports_a_stuck_iteration_once():
         w.resume()
     finally:
         w.stop()
+
+
+def test_transport_choice():
+    from gtopkssgd_b200.parallel.comm import choose_transport
+    one = ["a"] * 4
+    assert choose_transport("auto", one, [True] * 4) == "p2p"
+    assert choose_transport("auto", one, [True, True, False, True]) == "staged"      # no peer access somewhere
+    assert choose_transport("auto", ["a", "a", "b", "b"], [True] * 4) == "staged"    # two hosts
+    assert choose_transport("staged", one, [True] * 4) == "staged"
+    with pytest.raises(RuntimeError):
+        choose_transport("p2p", ["a", "b"], [True, True])
+    with pytest.raises(ValueError):
+        choose_transport("rdma", one, [True] * 4)

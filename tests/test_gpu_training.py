@@ -43,6 +43,17 @@ def test_two_gpu_training_matches_oracle(compressor):
 
 
 @pytest.mark.multigpu
+@pytest.mark.parametrize("compressor", ["gtopk", "topk2"])
+def test_two_gpu_staged_transport_matches_oracle(compressor):
+    """Ranks without GPU peer access (several hosts) exchange through the host
+    and gloo; forced here on one host."""
+    env = {"NCCL_NVLS_ENABLE": "0", "GTOPK_TRANSPORT": "staged"}
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 2, args=(4, 0.001, compressor, "cuda"), timeout_s=300,
+                         env=env)
+    replay_and_check(traces, 0.001, compressor, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.multigpu
 def test_four_gpu_gtopk_matches_oracle():
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
