@@ -79,6 +79,8 @@ def main():
     ap.add_argument("--threshold", type=int, default=None, help="merge threshold in elements (default: one group)")
     ap.add_argument("--channels-last", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--cudnn-benchmark-limit", type=int, default=None,
+                    help="how many algorithms cuDNN's autotuner tries per convolution (0 = all; default: PyTorch's 10)")
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="run every iteration eagerly instead of replaying the captured whole-iteration graph")
     args = ap.parse_args()
@@ -103,6 +105,8 @@ def main():
         _emit(real_stdout, {"error": "bench.py needs a CUDA device"})
         return 1
     torch.backends.cudnn.benchmark = True
+    if args.cudnn_benchmark_limit is not None:
+        torch.backends.cudnn.benchmark_limit = args.cudnn_benchmark_limit
     torch.backends.cudnn.allow_tf32 = False          # strict fp32, as the reference trains
     torch.backends.cuda.matmul.allow_tf32 = False
     local_rank = comm.env_local_rank()

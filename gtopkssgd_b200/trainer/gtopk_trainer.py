@@ -52,7 +52,7 @@ def _dump_profiling_norms(optimizer, rank, epoch):
 def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, compression=False,
                 compressor="topk", nwpernode=1, sigma_scale=2.5, pretrain=None, density=0.01, prefix=None,
                 max_iters=None, threshold=None, save_checkpoints=None, check_every=50, cuda_graph=None,
-                prefetch=None):
+                prefetch=None, membership_check_every=50):
     use_cuda = torch.cuda.is_available()
     rank = dopt.rank()
     if use_cuda:
@@ -80,7 +80,7 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
     optimizer = dopt.DistributedOptimizer(trainer.optimizer, trainer.net.named_parameters(), compression=comp,
                                           is_sparse=compression, err_handler=_error_handler, layerwise_times=None,
                                           sigma_scale=sigma_scale, density=density, norm_clip=None, writer=writer,
-                                          threshold=threshold)
+                                          threshold=threshold, membership_check_every=membership_check_every)
     trainer.update_optimizer(optimizer)
     iters_per_epoch = trainer.get_num_of_training_samples() // (nworkers * batch_size * nsteps_update)
     times, done = [], 0
@@ -124,10 +124,30 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
                 _dump_profiling_norms(optimizer, rank, epoch)
     except GTopkTimeout as exc:
         logger.error("training stopped: %s", exc)
+        _save_interrupted(trainer, exc)
         raise
     finally:
         optimizer.stop()
     return trainer
+
+
+def _save_interrupted(trainer, exc):
+    """A departure noticed on the host BEFORE an iteration was launched leaves
+    every surviving rank with the state of the last completed iteration:
+    write it out (weights, optimizer state, residuals) so that the job can be
+    restarted with ``--pretrain``.  After a device-side wait ran out in the
+    middle of an exchange the update may be partial, so nothing is saved."""
+    from ..parallel.elastic import PeerLeft
+    if not isinstance(exc.__cause__, PeerLeft):
+        return None
+    fn = os.path.join(trainer.checkpoint_dir(), "%s-rank%d-interrupted.pth" % (trainer.dnn, trainer.rank))
+    try:
+        trainer.save_checkpoint(trainer.make_checkpoint(full=True), fn)
+        logger.info("state of iteration %d saved to %s (restart with --pretrain)", trainer.train_iter, fn)
+        return fn
+    except Exception:  # never mask the communication failure
+        logger.exception("could not save the interrupted state")
+        return None
 
 
 def build_parser():

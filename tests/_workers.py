@@ -184,3 +184,45 @@ def failing_peer_worker(rank, world, mode):
         return "no error"
     except GTopkTimeout:
         return ("timeout", round(time.time() - t0, 1), calls)
+
+
+def interrupted_trainer_worker(rank, world, workdir):
+    """The gTop-k training driver on two gloo ranks; rank 1 finishes after two
+    iterations (an orderly departure), rank 0 wants ten.  Rank 0 must stop
+    with GTopkTimeout before launching its third iteration and leave the state
+    of iteration 2 on disk."""
+    import glob
+    import time
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.allreducer import GTopkTimeout
+    from gtopkssgd_b200.trainer import gtopk_trainer
+    from gtopkssgd_b200.trainer.dl_trainer import DLTrainer
+    os.makedirs(os.path.join(workdir, str(rank)), exist_ok=True)
+    os.chdir(os.path.join(workdir, str(rank)))
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("CRITICAL")
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=30)
+    if rank == 0:
+        orig = DLTrainer.train_step
+
+        def slow(self, *a, **k):
+            if self.train_iter == 2:
+                time.sleep(2.5)  # rank 1 has announced its departure by now
+            return orig(self, *a, **k)
+
+        DLTrainer.train_step = slow
+    args = dict(dnn="mnistnet", dataset="mnist", data_dir="synthetic", nworkers=world, lr=0.01, batch_size=4,
+                nsteps_update=1, max_epochs=1, compression=True, compressor="gtopk", density=0.01,
+                max_iters=2 if rank == 1 else 10, membership_check_every=1)
+    try:
+        gtopk_trainer.robust_ssgd(**args)
+    except GTopkTimeout as exc:
+        files = glob.glob(os.path.join("weights", "**", "*-interrupted.pth"), recursive=True)
+        ck = torch.load(files[0], map_location="cpu", weights_only=False) if files else {}
+        return {"error": str(exc), "files": files, "iter": ck.get("iter"),
+                "keys": sorted(ck.keys()), "n_resid": len(ck.get("residuals", {}))}
+    if rank == 1:
+        time.sleep(4.0)  # keep this process (and its connections) alive while rank 0 looks at the store
+    return {"finished": True}

@@ -99,3 +99,12 @@ def test_orderly_departure_is_seen_on_the_host_before_the_next_launch():
     kind, seconds, calls, msg = out[0]
     assert kind == "left-detected" and seconds < 2.0  # far below the 30 s wait limit
     assert calls == [(1, 0)] and "[1]" in msg
+
+
+def test_trainer_saves_state_when_a_peer_leaves(tmp_path):
+    out = spawn_ranks(_workers.interrupted_trainer_worker, 2, args=(str(tmp_path),), timeout_s=300)
+    assert out[1] == {"finished": True}
+    r0 = out[0]
+    assert "left the job" in r0["error"], r0
+    assert len(r0["files"]) == 1 and r0["iter"] == 2
+    assert {"epoch", "iter", "optimizer", "residuals", "state"} <= set(r0["keys"]) and r0["n_resid"] > 0
