@@ -344,6 +344,22 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             if n in self._flat.slots:
                 self._flat.residual_view(n).copy_(t)
 
+    def load_momentum_state(self, state):
+        """Velocity by parameter name (resuming a run): fills the flat momentum
+        buffer and marks the first step as done, so that the next step decays
+        the loaded velocity instead of re-initialising it with the gradient."""
+        hit = 0
+        with torch.no_grad():
+            for n, t in state.items():
+                if n in self._flat.slots and t is not None:
+                    self._flat.momentum_view(n).copy_(t)
+                    hit += 1
+        if hit:
+            self._step_count = max(self._step_count, 1)
+            for name, slot in self._flat.slots.items():
+                self.state[slot.param]["momentum_buffer"] = self._flat.momentum_view(name)
+        return hit
+
 
 def DistributedOptimizer(optimizer, named_parameters=None, compression=NoneCompressor, is_sparse=False,
                          err_handler=None, layerwise_times=None, sigma_scale=2.5, density=0.1, norm_clip=None,

@@ -87,6 +87,7 @@ class DLTrainer:
         self.ext = None
         self.use_cuda_graph = os.environ.get("GTOPK_CUDA_GRAPH", "0") == "1" if cuda_graph is None else bool(cuda_graph)
         self._copy_stream = None
+        self._pending_residuals = None
         self.prefetch_batches = os.environ.get("GTOPK_PREFETCH", "0") == "1"
         self._inflight = None
         self._graphed = None
@@ -192,7 +193,19 @@ class DLTrainer:
         return len(self.trainset)
 
     def update_optimizer(self, optimizer):
-        self.optimizer = optimizer
+        """Swap in the (wrapped) optimizer.  State that a checkpoint loaded
+        before the wrapping existed -- the velocity held by the plain optimizer
+        and the residuals, which only the wrapper can take -- moves over."""
+        old, self.optimizer = self.optimizer, optimizer
+        if old is not optimizer and hasattr(optimizer, "load_momentum_state"):
+            names = {p: n for n, p in self.net.named_parameters()}
+            bufs = {names[p]: st["momentum_buffer"] for p, st in old.state.items()
+                    if p in names and st.get("momentum_buffer") is not None}
+            if bufs:
+                optimizer.load_momentum_state(bufs)
+        if self._pending_residuals is not None and hasattr(optimizer, "load_residual_state"):
+            optimizer.load_residual_state(self._pending_residuals)
+            self._pending_residuals = None
 
     def update_model(self):
         self.optimizer.step()
@@ -220,8 +233,11 @@ class DLTrainer:
                 self.optimizer.load_state_dict(opt)
             except (ValueError, KeyError):
                 logger.warning("optimizer state in %s does not fit; ignored", filename)
-        if ckpt.get("residuals") is not None and hasattr(self.optimizer, "load_residual_state"):
-            self.optimizer.load_residual_state(ckpt["residuals"])
+        if ckpt.get("residuals") is not None:
+            if hasattr(self.optimizer, "load_residual_state"):
+                self.optimizer.load_residual_state(ckpt["residuals"])
+            else:
+                self._pending_residuals = ckpt["residuals"]  # handed to the wrapper in update_optimizer
         logger.info("Load pretrain model: %s, start from epoch %d and iter: %d", filename, self.train_epoch,
                     self.train_iter)
 

@@ -57,8 +57,11 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
     rank = dopt.rank()
     if use_cuda:
         torch.cuda.set_device(comm.env_local_rank() % max(torch.cuda.device_count(), 1))
-    if rank != 0:
-        pretrain = None
+    if rank != 0 and pretrain:
+        # weights come from rank 0's broadcast; a rank still reads its own file of the same checkpoint, if
+        # there is one, for what differs between ranks (the residuals)
+        own = pretrain.replace("-rank0-", "-rank%d-" % rank)
+        pretrain = own if own != pretrain and os.path.isfile(own) else None
     prefix = (prefix or settings.PREFIX) + "-ds%s" % str(density)
     trainer = DLTrainer(rank, nworkers, dist=False, batch_size=batch_size, is_weak_scaling=True,
                         ngpus=1 if use_cuda else 0, data_dir=data_dir, dataset=dataset, dnn=dnn, lr=lr,

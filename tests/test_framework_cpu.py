@@ -479,3 +479,38 @@ def test_transport_choice():
         choose_transport("p2p", ["a", "b"], [True, True])
     with pytest.raises(ValueError):
         choose_transport("rdma", one, [True] * 4)
+
+
+def test_resume_restores_velocity_and_residuals_through_the_wrapper(tmp_path, monkeypatch):
+    """A full checkpoint written by a wrapped trainer is loaded before the new
+    trainer's optimizer is wrapped; velocity and residuals must still arrive in
+    the flat buffers, and the next step must equal the uninterrupted run's."""
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+
+    def wrapped(pretrain=None):
+        t = _tiny_trainer(tmp_path, monkeypatch, dnn="mnistnet", dataset="mnist", pretrain=pretrain)
+        t.net.eval()  # no dropout noise: both runs see the same function
+        d = DistributedOptimizer(t.optimizer, t.net.named_parameters(), compression=compressors["gtopk"],
+                                 is_sparse=True, density=0.01)
+        t.update_optimizer(d)
+        return t, d
+
+    g = torch.Generator().manual_seed(5)
+    batches = [(torch.randn(4, 1, 28, 28, generator=g), torch.randint(0, 10, (4,), generator=g)) for _ in range(4)]
+    t, d = wrapped()
+    for b in batches[:3]:
+        t.train_step(data=b)
+    path = str(tmp_path / "full.pth")
+    t.save_checkpoint(t.make_checkpoint(full=True), path)
+    mom, res = d._flat.momentum.clone(), d._flat.residual.clone()
+    assert float(mom.abs().sum()) > 0 and float(res.abs().sum()) > 0
+    t.train_step(data=batches[3])
+    want = d._flat.param.clone()
+    d.stop()
+
+    t2, d2 = wrapped(pretrain=path)
+    assert t2.get_train_iter() == 3
+    assert torch.equal(d2._flat.momentum, mom) and torch.equal(d2._flat.residual, res)
+    t2.train_step(data=batches[3])
+    assert torch.allclose(d2._flat.param, want, rtol=1e-6, atol=1e-7)
+    d2.stop()
