@@ -14,6 +14,9 @@ residual.  Timed per call on the device (CUDA events, max over ranks):
              (the op sequence of allreducer.py:429-478 + 71-163; the unmodified
              reference cannot run here because mpi4py is absent)
 Roofline of the exchange: 2*k*log2(P)*8 bytes over one NVLink direction.
+With ``--prequeue`` a short bounded device-side delay is queued before the first
+event of every timed call (all arms alike), so that host launch work overlaps
+it, as it does in training where these launches sit behind backward.
 """
 from __future__ import annotations
 
@@ -26,6 +29,7 @@ import torch
 import torch.distributed as dist
 
 NVLINK_GBS = 770.0  # measured peer copy bandwidth per direction on this pool
+PREQUEUE_CYCLES = 0  # set by --prequeue
 
 
 def _timed(fn, iters, warmup, device, setup=None):
@@ -42,6 +46,8 @@ def _timed(fn, iters, warmup, device, setup=None):
         comm.barrier()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if PREQUEUE_CYCLES:
+            torch.cuda._sleep(PREQUEUE_CYCLES)
         a.record()
         fn()
         b.record()
@@ -133,7 +139,11 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-rehost", action="store_true")
     ap.add_argument("--json", type=str, default=None)
+    ap.add_argument("--prequeue", action="store_true",
+                    help="queue a bounded ~100 us device-side delay before each timed call (hides host launch work)")
     args = ap.parse_args()
+    global PREQUEUE_CYCLES
+    PREQUEUE_CYCLES = 200_000 if args.prequeue else 0
     settings.logger.setLevel("WARNING")
     if torch.cuda.is_available():
         torch.cuda.set_device(comm.env_local_rank() % torch.cuda.device_count())

@@ -4,7 +4,11 @@ latency of the emulated K2 exchange, timed with CUDA events after warm-up.
     python -m gtopkssgd_b200.bench_kernels [--sizes 16 64 138] [--densities 0.001 0.01] [--json out.json]
 
 Each timed iteration works on inputs larger than L2 (or L2 is flushed by
-writing a 256 MiB buffer first when they are not).  Roofline bytes: K1 12*d,
+writing a 256 MiB buffer first when they are not).  A short bounded device-side
+delay is queued in front of the first event, so that the host's launch work
+(Python, ctypes, driver: about 10 us) overlaps it instead of being counted as
+kernel time; in training these launches are queued behind backward in the same
+way (``--no-prequeue`` times from an idle GPU instead).  Roofline bytes: K1 12*d,
 K3 dense 16*d (8*d without momentum), K4 4*d.  Fractions are reported against
 the measured copy bandwidth in MEASURED_PEAKS.json when that file is present.
 """
@@ -32,6 +36,7 @@ class _Timer:
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
 
     iters, warmup = 10, 3
+    prequeue_cycles = 200_000  # about 100 us of bounded device-side spinning
 
     def time(self, fn, iters=None, warmup=None, setup=None):
         iters = iters or _Timer.iters
@@ -48,6 +53,8 @@ class _Timer:
             if self.flush_buf is not None:
                 self.flush_buf.fill_(1)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if _Timer.prequeue_cycles:
+                torch.cuda._sleep(_Timer.prequeue_cycles)
             a.record()
             fn()
             b.record()
@@ -154,8 +161,11 @@ def main():
                     help="which kernels to run (a small selection keeps a profiler capture short)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-prequeue", action="store_true", help="time from an idle GPU (includes host launch latency)")
     args = ap.parse_args()
     _Timer.iters, _Timer.warmup = args.iters, args.warmup
+    if args.no_prequeue:
+        _Timer.prequeue_cycles = 0
     peak = _peak_gbs()
     rows = []
     for m in args.sizes:

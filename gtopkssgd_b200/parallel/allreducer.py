@@ -86,6 +86,9 @@ class GroupEngine:
         self.resid = fb.group_slice(fb.residual, g) if fb.residual is not None else None
         self.numel = g.numel                # span in the flat buffers: what the kernels run over
         self.param_numel = g.param_numel    # number of parameters: what the density applies to
+        if self.numel >= 2 ** 31:
+            raise ValueError("merged group %d holds %d elements; the sparse pairs carry int32 indices, so a group must "
+                             "stay below 2^31 elements: lower the merge threshold" % (g.index, self.numel))
         self.last_k = 0
         self.result: Optional[SparseResult] = None
         self.dense_ready = False

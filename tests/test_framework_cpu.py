@@ -514,3 +514,15 @@ def test_resume_restores_velocity_and_residuals_through_the_wrapper(tmp_path, mo
     t2.train_step(data=batches[3])
     assert torch.allclose(d2._flat.param, want, rtol=1e-6, atol=1e-7)
     d2.stop()
+
+
+def test_group_size_limit_is_checked():
+    """int32 indices: a merged group of 2^31 elements or more is refused with a hint."""
+    from types import SimpleNamespace
+    from gtopkssgd_b200.parallel.allreducer import GroupEngine
+    from gtopkssgd_b200.parallel.flat_buffer import MergedGroup
+    g = MergedGroup(0, ["w"], 0, 2 ** 31, [0], "w", 2 ** 31)
+    fb = SimpleNamespace(grad=torch.zeros(1), residual=None, device=torch.device("cpu"),
+                         group_slice=lambda buf, grp: buf)
+    with pytest.raises(ValueError, match="2\\^31"):
+        GroupEngine(SimpleNamespace(flat=fb, mode="gtopk"), g)
