@@ -226,3 +226,27 @@ def interrupted_trainer_worker(rank, world, workdir):
     if rank == 1:
         time.sleep(4.0)  # keep this process (and its connections) alive while rank 0 looks at the store
     return {"finished": True}
+
+
+def flat_allreduce_worker(rank, world):
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel import flat_allreduce as fa
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=30)
+    torch.manual_seed(rank)  # different initial weights per rank: the wrapper must broadcast rank 0's
+    net = torch.nn.Sequential(torch.nn.Linear(6, 4), torch.nn.ReLU(), torch.nn.Linear(4, 2))
+    ddp = fa.DistributedDataParallel(net)
+    w0 = torch.cat([p.detach().flatten() for p in net.parameters()]).clone()
+    xs = [torch.full((3, 6), float(r + 1)) for r in range(world)]
+    ddp(xs[rank]).sum().backward()
+    fa.allreduce_gradients(net)
+    grad = torch.cat([p.grad.flatten() for p in net.parameters()]).clone()
+    # expected: mean over ranks of the local gradients, recomputed locally
+    acc = None
+    for r in range(world):
+        net.zero_grad()
+        net(xs[r]).sum().backward()
+        g = torch.cat([p.grad.flatten() for p in net.parameters()])
+        acc = g.clone() if acc is None else acc + g
+    comm.shutdown()
+    return {"grad": grad, "w0": w0, "expected": acc / world}

@@ -1,0 +1,120 @@
+"""CPU tests of the parts around the training path: extra model families, data
+preparation tools, the dependency-free dense wrapper, small utilities and the
+optional-dependency gates."""
+import os
+import wave
+
+import numpy as np
+import pytest
+import torch
+
+from gtopkssgd_b200.utils.launch import spawn_ranks
+
+import _workers
+
+
+@pytest.mark.parametrize("factory,kw", [("preresnet20", {}), ("resnet_mod20", {}), ("resnext29_8_64", {}),
+                                        ("densenet100_12", {}), ("caffe_cifar", {})])
+def test_extra_cifar_models_forward(factory, kw):
+    from gtopkssgd_b200.models import cifar_extras as ce
+    if not hasattr(ce, factory):
+        pytest.skip("no factory %s" % factory)
+    net = getattr(ce, factory)(num_classes=10, **kw)
+    net.eval()
+    with torch.no_grad():
+        out = net(torch.randn(2, 3, 32, 32))
+    out = out[0] if isinstance(out, (tuple, list)) else out
+    assert out.shape == (2, 10) and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("name,params", [("resnet18", 11689512), ("resnet34", 21797672), ("resnet50", 25557032)])
+def test_imagenet_resnet_parameter_counts(name, params):
+    from gtopkssgd_b200.models import imagenet_resnet as ir
+    net = getattr(ir, name)(num_classes=1000)
+    assert sum(p.numel() for p in net.parameters()) == params
+
+
+def test_raw_to_wav_and_an4_manifest(tmp_path):
+    from gtopkssgd_b200.data import prepare_audio as pa
+    assert pa.clean_an4_transcript("<s> hello world </s> (an4-x-1)") == "HELLO WORLD"
+    root = tmp_path / "an4"
+    for tag, folder in (("train", "an4_clstk"), ("test", "an4test_clstk")):
+        d = root / "wav" / folder / "spk"
+        d.mkdir(parents=True)
+        ids = []
+        for i, secs in enumerate((2.0, 0.3)):  # the second clip is shorter than the 1 s floor
+            samples = (np.sin(np.arange(int(16000 * secs)) * 0.05) * 8000).astype(">i2")
+            samples.tofile(d / ("u%d.raw" % i))
+            ids.append("%s/spk/u%d" % (folder, i))
+        (root / "etc").mkdir(exist_ok=True)
+        (root / "etc" / ("an4_%s.fileids" % tag)).write_text("\n".join(ids) + "\n")
+        (root / "etc" / ("an4_%s.transcription" % tag)).write_text(
+            "<s> one two </s> (u0)\n<s> three </s> (u1)\n")
+    target = tmp_path / "out"
+    pa.main(["an4", "--root", str(root), "--target", str(target)])
+    with wave.open(str(target / "train" / "an4" / "wav" / "u0.wav")) as w:
+        assert w.getframerate() == 16000 and w.getnframes() == 32000 and w.getsampwidth() == 2
+    assert (target / "train" / "an4" / "txt" / "u0.txt").read_text() == "ONE TWO"
+    train = (target / "an4_train_manifest.csv").read_text().strip().splitlines()
+    val = (target / "an4_val_manifest.csv").read_text().strip().splitlines()
+    assert len(train) == 1 and train[0].split(",")[0].endswith("u0.wav")   # pruned to [1, 15] seconds
+    assert len(val) == 2                                                   # the test split is not pruned
+
+
+def test_hdf5_converter_image_pipeline_and_gate(tmp_path):
+    from PIL import Image
+    from gtopkssgd_b200.data import create_hdf5 as ch
+    for split in ("train", "val"):
+        for cls in ("n01", "n02"):
+            d = tmp_path / split / cls
+            d.mkdir(parents=True)
+            Image.fromarray((np.random.rand(300, 500, 3) * 255).astype(np.uint8)).save(d / "a.jpeg")
+    items = ch.list_images(str(tmp_path / "train"), {"n01": 0, "n02": 1})
+    assert [y for _, y in items] == [0, 1]
+    img = ch.load_image(items[0][0])
+    assert img.shape == (224, 224, 3) and img.dtype == np.uint8
+    try:
+        import h5py  # noqa: F401
+    except ImportError:
+        with pytest.raises(ImportError):
+            ch.convert(str(tmp_path), str(tmp_path / "x.hdf5"))
+        from gtopkssgd_b200.data.datasets import DatasetHDF5
+        with pytest.raises(ImportError, match="h5py"):
+            DatasetHDF5(str(tmp_path / "x.hdf5"), "train")
+
+
+def test_small_utilities(tmp_path, monkeypatch):
+    from gtopkssgd_b200.utils import misc
+    monkeypatch.chdir(tmp_path)
+    assert len(misc.gen_random_id()) > 0 and misc.gen_random_id() != misc.gen_random_id()
+    p = misc.create_path("a/b/c")
+    assert os.path.isdir(p)
+    idx, val = misc.topk(np.array([0.1, -5.0, 3.0, -0.2]), 2)
+    assert set(idx.tolist()) == {1, 2} and set(val.tolist()) == {-5.0, 3.0}
+    d = {}
+    misc.force_insert_item(d, "k", 1)
+    misc.force_insert_item(d, "k", 2)
+    assert d == {"k": [1, 2]}
+
+
+def test_plots_gate_and_delta_helper(tmp_path):
+    from gtopkssgd_b200.analysis import plots
+    for e in range(2):
+        np.save(tmp_path / ("gtopknorm-rank0-epoch%d.npy" % e), np.array([1.0, 1.0]))
+        np.save(tmp_path / ("randknorm-rank0-epoch%d.npy" % e), np.array([2.0, 2.0]))
+    assert np.allclose(plots.delta_from_norm_files(str(tmp_path), 2), [0.25, 0.25])
+    try:
+        import matplotlib  # noqa: F401
+    except ImportError:
+        with pytest.raises(ImportError, match="matplotlib"):
+            plots.plot_delta(str(tmp_path), 2, str(tmp_path / "d.png"))
+    else:
+        assert os.path.isfile(plots.plot_delta(str(tmp_path), 2, str(tmp_path / "d.png")))
+
+
+def test_flat_allreduce_wrapper_two_ranks():
+    """The dependency-free dense wrapper: gradients are averaged over ranks,
+    weights start identical."""
+    out = spawn_ranks(_workers.flat_allreduce_worker, 2, timeout_s=120)
+    assert torch.allclose(out[0]["grad"], out[1]["grad"]) and torch.equal(out[0]["w0"], out[1]["w0"])
+    assert torch.allclose(out[0]["grad"], out[0]["expected"], atol=1e-6)
