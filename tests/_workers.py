@@ -250,3 +250,21 @@ def flat_allreduce_worker(rank, world):
         acc = g.clone() if acc is None else acc + g
     comm.shutdown()
     return {"grad": grad, "w0": w0, "expected": acc / world}
+
+
+def gtopk_world3_worker(rank, world):
+    from gtopkssgd_b200.models import create_net
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=30)
+    net, _ = create_net(10, "mnistnet")
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+    try:
+        DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True)
+        msg = "accepted"
+    except ValueError as exc:
+        msg = str(exc)
+    comm.shutdown()
+    return msg

@@ -108,3 +108,15 @@ def test_trainer_saves_state_when_a_peer_leaves(tmp_path):
     assert "left the job" in r0["error"], r0
     assert len(r0["files"]) == 1 and r0["iter"] == 2
     assert {"epoch", "iter", "optimizer", "residuals", "state"} <= set(r0["keys"]) and r0["n_resid"] > 0
+
+
+@pytest.mark.parametrize("compressor", ["topk", "topk2"])
+def test_three_workers_allgather_modes(compressor):
+    """The all-gather modes have no tree and run on any world size."""
+    traces = spawn_ranks(_workers.resnet20_gtopk_worker, 3, args=(2, 0.001, compressor), timeout_s=600)
+    replay_and_check(traces, 0.001, compressor)
+
+
+def test_three_workers_gtopk_is_refused():
+    out = spawn_ranks(_workers.gtopk_world3_worker, 3, timeout_s=120)
+    assert all("power-of-two" in o for o in out), out
