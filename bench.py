@@ -9,8 +9,9 @@ synthetic ImageNet-shaped data, plus the per-iteration communication time.
 Prints one JSON line on rank 0.  ``value`` is the whole-job samples/s timed on
 the device (CUDA events, barrier + synchronize on both sides, max over ranks)
 with the batch already resident on the GPU; ``e2e`` is the same loop through
-the public trainer API (``DLTrainer.train`` + ``update_model``) with the batch
-copied from pinned host memory every step and the loss read back every step.
+the public trainer API (``DLTrainer.prefetch`` + ``DLTrainer.train_step``): every
+step issues one copy of a batch from pinned host memory (the next step's
+inputs, on a copy stream) and ends with the loss read back to the host.
 ``--impl reference`` is the reference arm: it reports why the unmodified
 reference cannot run here.
 """
@@ -62,7 +63,8 @@ def reference_arm(args):
     reason = ("reference is not installable (no setup.py/pyproject.toml) and imports mpi4py, horovod and "
               "tensorboardX at module load, none of which exist in this image; it is also Python-2-only "
               "(dl_trainer.py:490 .next(), allreducer.py:115 range.index)")
-    print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+    if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also under torchrun
+        print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
     return 0
 
 
