@@ -105,3 +105,61 @@ def test_topk2_is_topk_of_sum():
     _, ref = torch.topk(dense.abs(), k)
     assert set(gi.tolist()) == set(ref.tolist())
     assert torch.allclose(dense[gi], gv, atol=1e-6)
+
+
+# ---- property tests (hypothesis): invariants of one gTop-k exchange for random sizes and worlds
+from hypothesis import given, settings as hsettings, strategies as hst  # noqa: E402
+
+
+@hsettings(max_examples=60, deadline=None)
+@given(logp=hst.integers(0, 3), d=hst.integers(8, 300), kfrac=hst.floats(0.01, 1.0), seed=hst.integers(0, 10 ** 6))
+def test_exchange_invariants(logp, d, kfrac, seed):
+    P = 1 << logp
+    k = max(int(d * kfrac), 1)
+    g = torch.Generator().manual_seed(seed)
+    grads = [torch.randn(d, generator=g) for _ in range(P)]
+    res_prev = [torch.randn(d, generator=g) * 0.1 for _ in range(P)]
+    res = [r.clone() for r in res_prev]
+    (gi, gv), local = oracle.simulate_gtopk_step(grads, res, k)
+    # the global set: at most k entries, each index once, drawn from the union of the local selections
+    assert gi.numel() <= k and gi.unique().numel() == gi.numel()
+    union = torch.cat([l[0] for l in local]).unique()
+    assert torch.isin(gi, union).all()
+    in_global = torch.zeros(d, dtype=torch.bool)
+    in_global[gi] = True
+    for p in range(P):
+        acc = grads[p] + res_prev[p]
+        li, lv = local[p]
+        assert li.numel() == min(k, d) and torch.equal(lv, acc[li])
+        # local selection = the k largest magnitudes of acc
+        kth = acc.abs().topk(min(k, d)).values.min()
+        mask = torch.zeros(d, dtype=torch.bool)
+        mask[li] = True
+        assert (acc.abs()[mask] >= kth).all() and (acc.abs()[~mask] <= kth).all()
+        # residual: 0 exactly where the entry was selected locally AND its index is in the global set
+        gone = mask & in_global
+        assert torch.equal(res[p][gone], torch.zeros(int(gone.sum())))
+        assert torch.equal(res[p][~gone], acc[~gone])
+    # a global value is the sum of the contributions that survived the tree; with k >= d nothing is cut
+    if k >= d:
+        dense = torch.zeros(d)
+        dense[gi] = gv
+        assert torch.allclose(dense, sum(gr + rp for gr, rp in zip(grads, res_prev)), atol=1e-5)
+    if P == 1:
+        assert set(gi.tolist()) == set(local[0][0].tolist())
+
+
+@hsettings(max_examples=30, deadline=None)
+@given(logp=hst.integers(1, 3), d=hst.integers(16, 200), seed=hst.integers(0, 10 ** 6))
+def test_identical_workers_agree_with_local_topk(logp, d, seed):
+    """All ranks hold the same gradient: the tree keeps exactly the local
+    selection and every value is P times the local one."""
+    P, k = 1 << logp, max(d // 8, 1)
+    g = torch.randn(d, generator=torch.Generator().manual_seed(seed))
+    res = [torch.zeros(d) for _ in range(P)]
+    (gi, gv), local = oracle.simulate_gtopk_step([g.clone() for _ in range(P)], res, k)
+    order, lorder = gi.argsort(), local[0][0].argsort()
+    assert torch.equal(gi[order], local[0][0][lorder])
+    assert torch.allclose(gv[order], P * local[0][1][lorder])
+    for r in res:  # nothing selected locally was dropped globally: the residual holds only unselected entries
+        assert torch.equal(r[gi], torch.zeros(gi.numel()))
