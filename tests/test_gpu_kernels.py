@@ -273,7 +273,7 @@ def test_region_guard_bands_detect_a_stray_write():
 
 
 @pytest.mark.parametrize("mode", ["topk", "topk2"])
-@pytest.mark.parametrize("P", [2, 4])
+@pytest.mark.parametrize("P", [2, 3, 4])  # the all-gather modes need no power-of-two world
 def test_k2t_allgather_emulated(P, mode):
     from gtopkssgd_b200.ops import exchange as ex
     from gtopkssgd_b200.ops.select import pairs_to_tensors
