@@ -150,6 +150,32 @@ def bench_k2_emulated(d: int, rho: float, world: int, nctas=None):
             "nctas": nctas or ex.default_nctas(k, world), "us": med * 1e6, "best_us": best * 1e6, "errors": bad}
 
 
+def bench_k2t_emulated(d: int, rho: float, world: int, reselect: bool):
+    """The all-gather exchange ('topk', or 'topk2' with reselect) for P ranks
+    emulated on one GPU in one cooperative launch."""
+    from .ops import exchange as ex
+    from .ops.select import TopkSelector
+    dev = torch.device("cuda")
+    k = max(int(d * rho), 1)
+    regions = ex.SymmetricRegion.create_emulated(world, ex.region_bytes(k, True), dev)
+    ranks = []
+    for r in range(world):
+        sel = TopkSelector(d, k, dev)
+        resid = torch.zeros(d, device=dev)
+        ranks.append(ex.ExchangeRank(r, world, d, k, sel, resid, regions[r], with_allgather=True, reselect=reselect))
+        sel.select(torch.randn(d, device=dev) * 0.1, resid, k)
+    desc = torch.cat([r.desc for r in ranks])
+    seg_counts = torch.zeros(world * ex.MAX_PEERS, dtype=torch.int32, device=dev)
+
+    def fn():
+        ex.launch_allgather(ranks, desc, seg_counts, 0, world, k, reselect=reselect)
+
+    med, best = _Timer(False).time(fn, iters=2 * _Timer.iters)
+    bad = [r.status() for r in ranks if r.status() != (0, 0)]
+    return {"kernel": "k2t_topk_allgather(emulated, %s)" % ("topk2" if reselect else "topk"), "d": d, "rho": rho,
+            "k": k, "P": world, "us": med * 1e6, "best_us": best * 1e6, "errors": bad}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes", type=float, nargs="*", default=[16, 64, 138], help="d in millions of elements")
@@ -189,6 +215,13 @@ def main():
             rows.append(bench_k2_emulated(d, 0.001, world))
             print(json.dumps(rows[-1]), flush=True)
             torch.cuda.empty_cache()
+    for m in (args.k2_sizes if "k2t" in args.only else []):
+        d = int(m * 1e6)
+        for world in args.worlds:
+            for reselect in (False, True):
+                rows.append(bench_k2t_emulated(d, 0.001, world, reselect))
+                print(json.dumps(rows[-1]), flush=True)
+                torch.cuda.empty_cache()
     if args.json:
         with open(args.json, "w") as fh:
             json.dump({"peak_hbm_gbs": peak, "rows": rows}, fh, indent=1)
