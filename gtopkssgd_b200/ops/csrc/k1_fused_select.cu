@@ -206,10 +206,13 @@ k1_fused(const float* __restrict__ g, float* __restrict__ r, const float* __rest
   }
   const float tau_used = st->tau;
   const float scale = g_scale ? *g_scale : 1.0f;
+  trace_stamp(ctrl, 0);
   stream_phase(*reinterpret_cast<StreamShared*>(smem_raw), g, r, scale, tau_used, cand, cap, ctrl, d);
 
+  trace_stamp(ctrl, 1);  // CTA 0 finished its share of the stream
   RankBarrier bar_all{ctrl, gridDim.x, 0u, limit_ns};
   if (!bar_all.sync(90)) return;
+  trace_stamp(ctrl, 2);  // every CTA did
   if (blockIdx.x == 0 && threadIdx.x == 0) st->n_calls = calls + 1u;
 
   SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
@@ -228,6 +231,7 @@ k1_fused(const float* __restrict__ g, float* __restrict__ r, const float* __rest
     auto key_at = [&](unsigned int i) -> uint32_t { return mag_key(ld_pair_cg(&cand[i]).val); };
     if (!radix_select_kth(s, bar, blockIdx.x, nct, C, k, ctrl->hist[0], key_at, &th, 100, true))
       return;
+    trace_stamp(ctrl, 3);  // k-th magnitude known
     StagedAppender app{&s, sel, &ctrl->cursor[0], k, ctrl};
     app.begin();
     const unsigned int stride = nct * kSelThreads;
@@ -245,6 +249,7 @@ k1_fused(const float* __restrict__ g, float* __restrict__ r, const float* __rest
       app.end_tile(none);
     }
     app.flush(none);
+    trace_stamp(ctrl, 4);  // CTA 0 compacted its share
     if (blockIdx.x == 0 && threadIdx.x == 0) {
       const float t_k = __uint_as_float(th.key);
       st->n_sel = k;
