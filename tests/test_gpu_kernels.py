@@ -52,6 +52,29 @@ def test_k1_select_matches_oracle(d, k):
     assert sel.stats()["n_calls"] == 4
 
 
+def test_k1_large_vector_dynamic_stream_pass():
+    """From 48 M elements on the stream pass hands its work out through a ticket
+    counter; compared here against the oracle computed on the device."""
+    d, k = 50_000_003, 50_000
+    torch.manual_seed(7)
+    sel = _selector(d, k)
+    r = torch.zeros(d, device=DEV)
+    for it in range(3):  # exact path, then predicted thresholds
+        g = torch.randn(d, device=DEV)
+        r_ref = r.clone()
+        idx_ref, val_ref = oracle.compress(g, r_ref, k)
+        sel.select(g, r, k)
+        idx, val = sel.pairs()
+        assert sel.status() == (0, 0) and idx.numel() == k
+        order, order_ref = idx.argsort(), idx_ref.argsort()
+        assert torch.equal(idx[order], idx_ref[order_ref])
+        assert torch.allclose(val[order], val_ref[order_ref], rtol=1e-6, atol=1e-7)
+        assert torch.allclose(r, r_ref, rtol=1e-6, atol=1e-7)
+        del g, r_ref
+    st = sel.stats()  # the residual grows over these calls, so a second exact pass is legitimate
+    assert st["n_calls"] == 3 and st["n_fallbacks"] < 3
+
+
 def test_k1_threshold_prediction_carries_steady_state():
     """With a stationary input distribution only the first call (no threshold
     yet) may take the exact dense path."""
