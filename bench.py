@@ -34,6 +34,7 @@ PUBLISHED_PER_WORKER = {
     "vgg16": {1: 1317.333, 4: 131.060, 8: 130.551},
     "resnet20": {1: 920.632, 4: 916.260, 8: 868.730},
     "lstm": {1: 392.0, 4: 17.8, 8: 17.6},
+    "alexnet": {1: 173.469, 4: 16.536, 8: 16.446},  # :487, batch 32 per worker
 }
 MODEL_DEFAULTS = {  # dataset, per-GPU batch, lr
     "resnet50": ("imagenet", 64, 0.1),
