@@ -201,3 +201,37 @@ class DeepSpeech(nn.Module):
         m = model.module if DeepSpeech.is_parallel(model) else model
         return {"version": m._version, "hidden_size": m._hidden_size, "hidden_layers": m._hidden_layers,
                 "rnn_type": supported_rnns_inv[m._rnn_type]}
+
+
+def describe_saved_model(path: str) -> dict:
+    """Metadata of a saved DeepSpeech package (what the reference prints from
+    ``python lstm_models.py --model-path ...``, lstm_models.py:324-364)."""
+    package = torch.load(path, map_location="cpu", weights_only=False)
+    model = DeepSpeech.load_model_package(package)
+    info = {"model": model.__class__.__name__, "version": package.get("version"),
+            "rnn_type": package["rnn_type"], "rnn_layers": package["hidden_layers"],
+            "rnn_size": package["hidden_size"], "bidirectional": package.get("bidirectional", True),
+            "classes": len(package["labels"]), "labels": package["labels"],
+            "parameters": DeepSpeech.get_param_size(model), "audio_conf": package.get("audio_conf", {})}
+    for key in ("epoch", "iteration", "avg_loss"):
+        if package.get(key) is not None:
+            info[key] = package[key]
+    if package.get("loss_results") is not None:
+        epochs = package.get("epoch", len(package["loss_results"]))
+        info["training"] = [{"epoch": i + 1, "loss": float(package["loss_results"][i]),
+                             "wer": float(package["wer_results"][i]), "cer": float(package["cer_results"][i])}
+                            for i in range(min(int(epochs), len(package["loss_results"])))]
+    return info
+
+
+def main(argv=None):
+    import argparse
+    import json
+    ap = argparse.ArgumentParser(description="Print the metadata of a saved DeepSpeech model")
+    ap.add_argument("--model-path", required=True)
+    args = ap.parse_args(argv)
+    print(json.dumps(describe_saved_model(args.model_path), indent=1, default=str))
+
+
+if __name__ == "__main__":
+    main()

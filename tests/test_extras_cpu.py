@@ -118,3 +118,22 @@ def test_flat_allreduce_wrapper_two_ranks():
     out = spawn_ranks(_workers.flat_allreduce_worker, 2, timeout_s=120)
     assert torch.allclose(out[0]["grad"], out[1]["grad"]) and torch.equal(out[0]["w0"], out[1]["w0"])
     assert torch.allclose(out[0]["grad"], out[0]["expected"], atol=1e-6)
+
+
+def test_deepspeech_package_roundtrip_and_description(tmp_path):
+    from gtopkssgd_b200.models import lstm_models as lm
+    labels = "_'ABC "
+    net = lm.DeepSpeech(rnn_hidden_size=16, nb_layers=2, labels=labels, audio_conf={"sample_rate": 16000,
+                        "window_size": 0.02, "window_stride": 0.01, "window": "hamming"}, bidirectional=True)
+    pkg = lm.DeepSpeech.serialize(net, epoch=1, iteration=7, avg_loss=1.5, loss_results=[3.0, 2.0],
+                                  cer_results=[50.0, 40.0], wer_results=[90.0, 80.0])
+    path = tmp_path / "ds.pth"
+    torch.save(pkg, path)
+    again = lm.DeepSpeech.load_model(str(path))
+    for (k, a), (_, b) in zip(net.state_dict().items(), again.state_dict().items()):
+        assert torch.equal(a, b), k
+    info = lm.describe_saved_model(str(path))
+    assert info["rnn_layers"] == 2 and info["rnn_size"] == 16 and info["classes"] == len(labels)
+    assert info["parameters"] == lm.DeepSpeech.get_param_size(net) and info["epoch"] == 2
+    assert info["training"][1] == {"epoch": 2, "loss": 2.0, "wer": 80.0, "cer": 40.0}
+    lm.main(["--model-path", str(path)])
