@@ -112,9 +112,12 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             (self._watchdog.pause if value else self._watchdog.resume)()
 
     def _on_stall(self, seconds: float) -> None:
+        """Runs on the watchdog thread: only logs and leaves a note; err_handler
+        (which may rebuild the trainer's data loaders) is called from the
+        training thread, in pre_iteration()."""
         msg = "device work of iteration %d still running after %.0f s" % (self._allreducer.train_iter, seconds)
+        logger.error("watchdog: %s", msg)
         self._stalled = msg
-        self._allreducer.report_failure(msg)
 
     def post_iteration(self) -> None:
         """Everything of an iteration has been enqueued: hand the watchdog an
@@ -172,6 +175,7 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         instead of a device-side wait running out later."""
         if self._stalled is not None and not self.capturing:
             msg, self._stalled = self._stalled, None
+            self._allreducer.report_failure(msg)
             raise ar.GTopkTimeout(msg)
         m = self._membership
         if m is None or self.capturing:

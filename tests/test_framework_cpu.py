@@ -526,3 +526,22 @@ def test_group_size_limit_is_checked():
                          group_slice=lambda buf, grp: buf)
     with pytest.raises(ValueError, match="2\\^31"):
         GroupEngine(SimpleNamespace(flat=fb, mode="gtopk"), g)
+
+
+def test_watchdog_note_is_raised_on_the_training_thread(monkeypatch):
+    """A stall seen by the watchdog thread is only noted there; err_handler and
+    GTopkTimeout happen at the next pre_iteration() of the training thread."""
+    from gtopkssgd_b200.parallel.allreducer import GTopkTimeout
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+    net, _ = create_net(10, "mnistnet")
+    calls = []
+    opt = torch.optim.SGD(net.parameters(), lr=0.01)
+    d = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                             density=0.01, err_handler=lambda n, r: calls.append((n, r)))
+    d._on_stall(123.0)
+    assert calls == [] and d._stalled is not None
+    with pytest.raises(GTopkTimeout, match="still running after 123 s"):
+        d.zero_grad()
+    assert calls == [(1, 0)]
+    d.zero_grad()  # the note is consumed
+    d.stop()
