@@ -37,14 +37,17 @@ constexpr int kWarpFlushAt = kWarpStage - 32;
 // it the static split is faster (measured: +3.6 % at 138 M and +1.5 % at 64 M, but -4 % at 25.6 M).
 constexpr long long kDynamicMinVec = 12ll * 1000 * 1000;
 
+constexpr int kPredDigits = 3;  // second-digit histograms are kept for the predicted first digit and its neighbours
 struct StreamShared {
   Pair wstage[kK1Threads / 32][kWarpStage];  // per-warp candidate staging
   unsigned int hist[kHistBins];              // first radix digit of this CTA's candidates
+  unsigned int hist1[kPredDigits][1024];     // second digit of the candidates whose first digit is pred-1, pred, pred+1
 };
 constexpr size_t kK1SmemBytes =
     sizeof(StreamShared) > sizeof(SelectShared) ? sizeof(StreamShared) : sizeof(SelectShared);
-// bytes of a control block that K1 dirties: header, trace, two histogram sets
-constexpr size_t kK1ClearBytes = offsetof(Ctrl, hist) + 2 * sizeof(((Ctrl*)0)->hist[0]);
+// bytes of a control block that K1 dirties: header, trace, three histogram sets
+// (set 0: candidate select, set 1: exact mode, set 2: second-digit histograms built by the stream pass)
+constexpr size_t kK1ClearBytes = offsetof(Ctrl, hist) + 3 * sizeof(((Ctrl*)0)->hist[0]);
 
 __device__ __forceinline__ void warp_flush(Pair* wbuf, unsigned int& wcnt, Pair* cand,
                                            unsigned int cap, unsigned int* counter, float* r) {
@@ -64,12 +67,24 @@ __device__ __forceinline__ void warp_flush(Pair* wbuf, unsigned int& wcnt, Pair*
   __syncwarp();
 }
 
+// Counts one candidate: its first radix digit always, its second digit when the
+// first one is within one of `pred` (the first digit of the previous call's k-th
+// magnitude), so that the candidate select can usually skip its first sweep.
+__device__ __forceinline__ void count_candidate(StreamShared& ss, float a, unsigned int pred) {
+  const uint32_t key = mag_key(a);
+  const unsigned int fd = key >> 20;
+  atomicAdd(&ss.hist[fd], 1u);
+  const unsigned int off = fd - pred + 1u;  // wraps for fd < pred - 1: then off >= kPredDigits
+  if (off < (unsigned int)kPredDigits) atomicAdd(&ss.hist1[off][(key >> 10) & 1023u], 1u);
+}
+
 // One tile of the stream pass: kK1Vec float4 of g and of r per thread, STRIDE
 // float4 apart (the CTA's 512 threads or one warp's 32 lanes work side by side).
 template <int STRIDE>
 __device__ __forceinline__ void stream_tile(long long v0, long long nvec, long long head,
                                             const float4* __restrict__ g4, float4* __restrict__ r4,
-                                            float scale, float tau, StreamShared& ss, Pair* wbuf,
+                                            float scale, float tau, unsigned int pred, StreamShared& ss,
+                                            Pair* wbuf,
                                             unsigned int& wcnt, Pair* __restrict__ cand, unsigned int cap,
                                             unsigned int* counter, float* __restrict__ r) {
   float4 gv[kK1Vec], rv[kK1Vec];
@@ -115,7 +130,7 @@ __device__ __forceinline__ void stream_tile(long long v0, long long nvec, long l
             p.idx = (int32_t)(head + (v << 2) + e);
             p.val = a[e];
             wbuf[wcnt + __popc(m & lanemask_lt())] = p;
-            atomicAdd(&ss.hist[mag_key(a[e]) >> 20], 1u);
+            count_candidate(ss, a[e], pred);
           }
           wcnt += __popc(m);
           if (wcnt > (unsigned int)kWarpFlushAt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
@@ -128,8 +143,9 @@ __device__ __forceinline__ void stream_tile(long long v0, long long nvec, long l
 __device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __restrict__ g,
                                              float* __restrict__ r, float scale, float tau,
                                              Pair* __restrict__ cand, unsigned int cap, Ctrl* ctrl,
-                                             long long d) {
+                                             long long d, unsigned int pred) {
   for (int i = threadIdx.x; i < kHistBins; i += kK1Threads) ss.hist[i] = 0u;
+  for (int i = threadIdx.x; i < kPredDigits * 1024; i += kK1Threads) (&ss.hist1[0][0])[i] = 0u;
   __syncthreads();
   Pair* wbuf = ss.wstage[threadIdx.x >> 5];
   unsigned int wcnt = 0;
@@ -148,9 +164,11 @@ __device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __re
   constexpr long long kWarpTileVec = 32ll * kK1Vec;
   if (nvec < kDynamicMinVec) {
     // Static split: CTA b takes tiles b, b + grid, ...; every load instruction of the CTA covers 8 KB.
+    // (One contiguous, equally sized range per CTA was tried: its ragged last tile costs almost a full
+    // tile's latency in every CTA, and the call got 3 % slower at d = 25.6 M.)
     const long long ntiles = (nvec + kTileVec - 1) / kTileVec;
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
-      stream_tile<kK1Threads>(tile * kTileVec + threadIdx.x, nvec, head, g4, r4, scale, tau, ss, wbuf, wcnt,
+      stream_tile<kK1Threads>(tile * kTileVec + threadIdx.x, nvec, head, g4, r4, scale, tau, pred, ss, wbuf, wcnt,
                               cand, cap, counter, r);
   } else {
     // Large vectors: SMs do not all see the same memory bandwidth, and with the static split the grid
@@ -169,7 +187,8 @@ __device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __re
       for (long long wt = 0; wt < kChunkTiles; ++wt) {
         const long long base = (chunk * kChunkTiles + wt) * kWarpTileVec;
         if (base >= nvec) break;  // warp-uniform
-        stream_tile<32>(base + lane_id(), nvec, head, g4, r4, scale, tau, ss, wbuf, wcnt, cand, cap, counter, r);
+        stream_tile<32>(base + lane_id(), nvec, head, g4, r4, scale, tau, pred, ss, wbuf, wcnt, cand, cap, counter,
+                        r);
       }
       nxt = __shfl_sync(0xffffffffu, nxt, 0);
       chunk = (long long)nwarps_grid + nxt;
@@ -196,7 +215,7 @@ __device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __re
           p.idx = (int32_t)i;
           p.val = a;
           wbuf[wcnt + __popc(m & lanemask_lt())] = p;
-          atomicAdd(&ss.hist[mag_key(a) >> 20], 1u);
+          count_candidate(ss, a, pred);
         }
         wcnt += __popc(m);
         if (wcnt > (unsigned int)kWarpFlushAt) warp_flush(wbuf, wcnt, cand, cap, counter, r);
@@ -209,6 +228,10 @@ __device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __re
   for (int i = threadIdx.x; i < kHistBins; i += kK1Threads) {
     const unsigned int c = ss.hist[i];
     if (c) atomicAdd(&ctrl->hist[0][0][i], c);
+  }
+  for (int i = threadIdx.x; i < kPredDigits * 1024; i += kK1Threads) {
+    const unsigned int c = ss.hist1[i >> 10][i & 1023];
+    if (c) atomicAdd(&ctrl->hist[2][i >> 10][i & 1023], c);
   }
 }
 
@@ -246,7 +269,8 @@ k1_fused(const float* __restrict__ g, float* __restrict__ r, const float* __rest
   const float tau_used = st->tau;
   const float scale = g_scale ? *g_scale : 1.0f;
   trace_stamp(ctrl, 0);
-  stream_phase(*reinterpret_cast<StreamShared*>(smem_raw), g, r, scale, tau_used, cand, cap, ctrl, d);
+  const unsigned int pred = mag_key(st->kth_mag) >> 20;  // first digit of the previous call's k-th magnitude
+  stream_phase(*reinterpret_cast<StreamShared*>(smem_raw), g, r, scale, tau_used, cand, cap, ctrl, d, pred);
 
   trace_stamp(ctrl, 1);  // CTA 0 finished its share of the stream
   RankBarrier bar_all{ctrl, gridDim.x, 0u, limit_ns};
@@ -268,7 +292,8 @@ k1_fused(const float* __restrict__ g, float* __restrict__ r, const float* __rest
     if (blockIdx.x >= nct) return;
     RankBarrier bar{ctrl, nct, 0u, limit_ns, &ctrl->scratch[0]};
     auto key_at = [&](unsigned int i) -> uint32_t { return mag_key(ld_pair_cg(&cand[i]).val); };
-    if (!radix_select_kth(s, bar, blockIdx.x, nct, C, k, ctrl->hist[0], key_at, &th, 100, true))
+    if (!radix_select_kth(s, bar, blockIdx.x, nct, C, k, ctrl->hist[0], key_at, &th, 100, true, ctrl->hist[2],
+                          pred - 1u, kPredDigits))
       return;
     trace_stamp(ctrl, 3);  // k-th magnitude known
     StagedAppender app{&s, sel, &ctrl->cursor[0], k, ctrl};

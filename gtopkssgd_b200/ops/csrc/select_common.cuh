@@ -105,14 +105,19 @@ __device__ __forceinline__ void find_digit(SelectShared& s, const unsigned int* 
 // key_at(i) returns the 31-bit magnitude key of entry i, or 0xffffffff for a dead
 // entry.  hist points to three zeroed global histograms [3][kHistBins].
 // have_pass0: hist[0] already holds the complete first-digit histogram of the
-// entries (an earlier kernel built it), so the first sweep is skipped.
+// entries (an earlier phase built it), so the first sweep is skipped.
+// pre1 / pre1_lo / pre1_n: complete second-digit histograms (1024 bins each) of
+// the entries whose first digit is pre1_lo, pre1_lo + 1, ..., pre1_lo + pre1_n - 1;
+// if the threshold's first digit is one of them the second sweep is skipped too.
 // Returns false on abort.
 template <typename KeyAt>
 __device__ __forceinline__ bool radix_select_kth(SelectShared& s, RankBarrier& bar, unsigned int cta,
                                                  unsigned int nctas, unsigned int n, unsigned int k,
                                                  unsigned int (*hist)[kHistBins], KeyAt key_at,
                                                  Threshold* out, uint32_t where,
-                                                 bool have_pass0 = false) {
+                                                 bool have_pass0 = false,
+                                                 unsigned int (*pre1)[kHistBins] = nullptr,
+                                                 unsigned int pre1_lo = 0u, unsigned int pre1_n = 0u) {
   const unsigned int stride = nctas * kSelThreads;
   uint32_t prefix = 0;
   unsigned int k_rem = k;
@@ -139,14 +144,19 @@ __device__ __forceinline__ bool radix_select_kth(SelectShared& s, RankBarrier& b
   k_rem = s.res_krem;
   __syncthreads();
   // pass 1: bits 19..10
-  smem_hist_clear(s);
-  for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride) {
-    const uint32_t key = key_at(i);
-    if (key != 0xffffffffu && (key >> 20) == prefix) atomicAdd(&s.hist[(key >> 10) & 1023u], 1u);
+  const unsigned int pre_off = prefix - pre1_lo;  // wraps when prefix < pre1_lo
+  if (pre1 != nullptr && pre_off < pre1_n) {
+    find_digit<1024>(s, pre1[pre_off], k_rem, false);  // built earlier: no sweep, no barrier
+  } else {
+    smem_hist_clear(s);
+    for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride) {
+      const uint32_t key = key_at(i);
+      if (key != 0xffffffffu && (key >> 20) == prefix) atomicAdd(&s.hist[(key >> 10) & 1023u], 1u);
+    }
+    if (!local) smem_hist_flush(s, hist[1], 1024);
+    if (!bar.sync(where + 1)) return false;
+    find_digit<1024>(s, hist[1], k_rem, local);
   }
-  if (!local) smem_hist_flush(s, hist[1], 1024);
-  if (!bar.sync(where + 1)) return false;
-  find_digit<1024>(s, hist[1], k_rem, local);
   prefix = (prefix << 10) | s.res_digit;
   k_rem = s.res_krem;
   __syncthreads();
