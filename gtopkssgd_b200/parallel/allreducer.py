@@ -12,8 +12,10 @@ What changes: a group is a slice of the flat gradient buffer (no merge copy);
 soon as the group's last gradient has been produced, and nothing synchronises
 the device.  The result of a sparse reduction stays sparse: ``SparseResult``
 hands K3 the k global pairs.  On CUDA with more than one rank the exchange is
-the persistent peer-store kernel (no MPI, no NCCL, no host staging); on CPU it
-is the gloo fallback, which is also the oracle.
+the persistent peer-store kernel (no MPI, no NCCL, no host staging) when all
+ranks share a host and have GPU peer access, else the selection is staged
+through the host and gloo; on CPU it is the gloo fallback, which is also the
+oracle.
 """
 from __future__ import annotations
 
