@@ -411,6 +411,21 @@ class AllReducer:
                     self.reset()
                     self._msg_queue2.put("DONE")
 
+    def rebuild(self) -> None:
+        """The process group changed (a smaller world after a planned
+        departure): release what was tied to the old one and build the group
+        engines again.  Gradients, residuals, parameters and momentum live in
+        the flat buffers and are untouched; the selectors start again with an
+        exact pass.  gTop-k needs a power-of-two world: on any other size the
+        job continues with 'topk2' (all-gather, sum, global re-selection)."""
+        self.stop()
+        self._failed = None
+        world = comm.size()
+        if self.mode == "gtopk" and world & (world - 1):
+            logger.warning("%d workers left: gTop-k needs a power of two, continuing with topk2", world)
+            self.mode = "topk2"
+        self.engines = [GroupEngine(self, g) for g in self.flat.groups]
+
     def stop(self) -> None:
         self._running = False
         for e in self.engines:

@@ -16,6 +16,7 @@ import torch
 import torch.distributed as dist
 
 _cpu_group = None
+_hosts: list = []  # host name of every rank of the group formed by init()
 
 
 def env_rank() -> int:
@@ -34,7 +35,7 @@ def init(backend: Optional[str] = None, timeout_s: float = 1800.0, device: Optio
     """Join the process group described by RANK / WORLD_SIZE / MASTER_* (the
     torchrun contract).  Does nothing for a single process or when the group
     already exists."""
-    global _cpu_group
+    global _cpu_group, _hosts
     if env_world_size() <= 1 or dist.is_initialized():
         return
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -50,11 +51,55 @@ def init(backend: Optional[str] = None, timeout_s: float = 1800.0, device: Optio
                             timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
     if backend == "nccl":
         _cpu_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
+    import socket
+    _hosts = [None] * env_world_size()
+    dist.all_gather_object(_hosts, socket.gethostname(), group=_cpu_group)
 
 
 def cpu_group():
     """A gloo group for host-side object exchange (None = the default group)."""
     return _cpu_group
+
+
+_generation = 0
+
+
+def reform(survivors, timeout_s: float = 120.0):
+    """Leave the current process group and form a new one of the surviving
+    ranks (``survivors``: old rank numbers, the same list on every survivor).
+    Called between two iterations, with no collective in flight and after the
+    departing ranks have stopped taking part.  The new rank 0 (the lowest
+    surviving old rank) hosts the new rendezvous store on MASTER_PORT + 17 +
+    generation.  Returns (new_rank, new_world)."""
+    global _cpu_group, _transport, _generation
+    survivors = sorted(int(r) for r in survivors)
+    old_rank = rank()
+    if old_rank not in survivors:
+        raise ValueError("rank %d is not among the survivors %s" % (old_rank, survivors))
+    backend = dist.get_backend()
+    new_rank, new_world = survivors.index(old_rank), len(survivors)
+    master = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    if _hosts and len(set(_hosts)) > 1:
+        master = _hosts[survivors[0]]
+    _generation += 1
+    port = int(os.environ.get("MASTER_PORT", "29500")) + 17 + _generation
+    dist.destroy_process_group()
+    _cpu_group, _transport = None, None
+    if _hosts:
+        _hosts[:] = [_hosts[r] for r in survivors]
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = str(new_rank), str(new_world)
+    if new_world == 1:
+        return 0, 1
+    store = dist.TCPStore(master, port, new_world, is_master=(new_rank == 0),
+                          timeout=datetime.timedelta(seconds=timeout_s))
+    kwargs: Dict[str, Any] = {}
+    if backend == "nccl":
+        kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group(backend=backend, store=store, rank=new_rank, world_size=new_world,
+                            timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    if backend == "nccl":
+        _cpu_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
+    return new_rank, new_world
 
 
 def choose_transport(requested: str, hosts, peer_ok) -> str:

@@ -42,8 +42,12 @@ from .flat_buffer import FlatBuffers
 class _DistributedOptimizer(torch.optim.Optimizer):
     def __init__(self, params, named_parameters, compressor, is_sparse=True, err_handler=None, layerwise_times=None,
                  sigma_scale=2.5, density=0.01, norm_clip=None, writer=None, threshold=None, overlap=True,
-                 wait_limit_ms=None, membership_check_every=50):
+                 wait_limit_ms=None, membership_check_every=50, elastic=False):
         super(self.__class__, self).__init__(params)
+        self.elastic = bool(elastic)
+        self.generation = 0        # bumped whenever the process group is re-formed (captured graphs are stale then)
+        self.leave_at: Optional[int] = None
+        self._membership_check_every = membership_check_every
         self._compressor = compressor
         self._sparse = is_sparse
         self._layerwise_times = layerwise_times
@@ -183,6 +187,9 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         try:
             m.check(self._allreducer.train_iter)
         except PeerLeft as exc:
+            if self.elastic and exc.planned:
+                self._shrink(exc.ranks)
+                return
             a = self._allreducer
             a._failed = str(exc)
             logger.error("membership: %s", exc)
@@ -191,6 +198,52 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             except Exception:
                 logger.exception("err_callback raised")
             raise ar.GTopkTimeout(str(exc)) from exc
+
+    # -- elastic: planned departures ------------------------------------------------
+    def request_leave(self) -> Optional[int]:
+        """This rank wants to leave (a pre-emption notice, a drained node).  It
+        announces the iteration from which it no longer takes part and must
+        keep training until ``should_exit()`` turns true.  Returns that
+        iteration, or None when there is nobody to tell."""
+        if self._membership is None:
+            self.leave_at = self._allreducer.train_iter
+            return self.leave_at
+        if self.leave_at is None:
+            self.leave_at = self._membership.announce_leave(self._allreducer.train_iter)
+            logger.info("leaving the job before iteration %d", self.leave_at)
+        return self.leave_at
+
+    def should_exit(self) -> bool:
+        return self.leave_at is not None and self._allreducer.train_iter >= self.leave_at
+
+    def _shrink(self, gone) -> None:
+        """Every survivor arrives here at the same iteration, before launching
+        anything of it: re-form the process group without the departed ranks,
+        rebuild the exchange for the new world and tell the trainer, which
+        re-shards its data (err_handler(new_size, new_rank))."""
+        a = self._allreducer
+        old_world = a.size()
+        survivors = [r for r in range(old_world) if r not in set(gone)]
+        if self._is_cuda:
+            torch.cuda.synchronize()
+        if self._watchdog is not None:
+            self._watchdog.disarm()
+        for e in a.engines:  # peer mappings of the old world go first, while every mapped buffer still exists
+            region = getattr(e, "region", None)
+            if region is not None:
+                region.close()
+                e.region = None
+        new_rank, new_world = comm.reform(survivors)
+        a.rebuild()
+        self._membership = Membership.for_default_group(check_every=self._membership_check_every) \
+            if self._membership_check_every else None
+        self.generation += 1
+        logger.warning("ranks %s left: continuing with %d workers as rank %d (%s)", list(gone), new_world, new_rank,
+                       a.mode)
+        try:
+            a._err_callback(new_world, new_rank)
+        except Exception:
+            logger.exception("err_callback raised")
 
     def zero_grad(self, set_to_none: bool = False):
         """Clears the flat gradient buffer with one fill; ``p.grad`` stay views."""
@@ -367,13 +420,15 @@ class _DistributedOptimizer(torch.optim.Optimizer):
 
 def DistributedOptimizer(optimizer, named_parameters=None, compression=NoneCompressor, is_sparse=False,
                          err_handler=None, layerwise_times=None, sigma_scale=2.5, density=0.1, norm_clip=None,
-                         writer=None, threshold=None, overlap=True, wait_limit_ms=None, membership_check_every=50):
+                         writer=None, threshold=None, overlap=True, wait_limit_ms=None, membership_check_every=50,
+                         elastic=False):
     """Wrap ``optimizer``.  The returned object is an instance of a subclass of
     ``type(optimizer)`` that carries the methods above."""
     cls = type(optimizer.__class__.__name__, (optimizer.__class__,), dict(_DistributedOptimizer.__dict__))
     return cls(optimizer.param_groups, named_parameters, compression, is_sparse, err_handler, layerwise_times,
                sigma_scale=sigma_scale, density=density, norm_clip=norm_clip, writer=writer, threshold=threshold,
-               overlap=overlap, wait_limit_ms=wait_limit_ms, membership_check_every=membership_check_every)
+               overlap=overlap, wait_limit_ms=wait_limit_ms, membership_check_every=membership_check_every,
+               elastic=elastic)
 
 
 def rank():

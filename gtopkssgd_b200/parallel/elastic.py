@@ -19,11 +19,15 @@ import torch.distributed as dist
 
 
 class PeerLeft(RuntimeError):
-    """One or more ranks left the job (or stopped beating)."""
+    """One or more ranks left the job (or stopped beating).  ``planned`` is set
+    when every survivor learns of the departure at the same iteration (the
+    leaver announced it ahead of time), which is what re-forming a smaller job
+    needs."""
 
-    def __init__(self, ranks: List[int], why: str):
+    def __init__(self, ranks: List[int], why: str, planned: bool = False):
         super().__init__("ranks %s %s" % (ranks, why))
         self.ranks = ranks
+        self.planned = planned
 
 
 def default_store():
@@ -43,6 +47,9 @@ class Membership:
         self.stale_after_s, self.check_every = stale_after_s, max(int(check_every), 1)
         self._calls = 0
         self._left_sent = False
+        self._leave_at: Optional[int] = None
+        self._planned: dict = {}
+        self._dropped: set = set()
         if store is not None:
             self.beat(0)
 
@@ -66,9 +73,27 @@ class Membership:
                 pass  # the store's host may already be gone at shutdown
             self._left_sent = True
 
+    def announce_leave(self, step: int) -> int:
+        """Planned departure: this rank keeps working up to, and not including,
+        the returned iteration.  That iteration is the second next check point
+        of the survivors, so each of them reads the announcement at the check
+        point in between and all of them drop this rank at the same iteration."""
+        ce = self.check_every
+        at = (step // ce + 2) * ce
+        self.store.set("leave_at/%d" % self.rank, str(at))
+        self._leave_at = at
+        return at
+
     # -- the others ---------------------------------------------------------------------------
     def departed(self) -> List[int]:
         return [q for q in range(self.world) if q != self.rank and self.store.check(["left/%d" % q])]
+
+    def planned(self) -> dict:
+        """{rank: iteration} of the announced departures seen so far."""
+        for q in range(self.world):
+            if q != self.rank and q not in self._planned and self.store.check(["leave_at/%d" % q]):
+                self._planned[q] = int(self.store.get("leave_at/%d" % q).decode())
+        return self._planned
 
     def stale(self, now: Optional[float] = None) -> List[int]:
         now = time.time() if now is None else now
@@ -86,10 +111,17 @@ class Membership:
         Every ``check_every`` calls: beat, then raise PeerLeft if somebody left
         or went silent."""
         self._calls += 1
-        if not force and self._calls % self.check_every:
+        due = sorted(q for q, at in self._planned.items() if step >= at)
+        if due:  # announced earlier, effective now: the same on every survivor
+            for q in due:
+                del self._planned[q]
+            self._dropped.update(due)
+            raise PeerLeft(due, "left the job as announced", planned=True)
+        if not force and step % self.check_every:
             return
         self.beat(step)
-        gone = self.departed()
+        self.planned()
+        gone = [q for q in self.departed() if q not in self._dropped]
         if gone:
             raise PeerLeft(gone, "left the job")
         silent = self.stale()

@@ -28,6 +28,7 @@ class GraphedStep:
         self.clip_norm = clip_norm
         self.warmup = warmup
         self.eager_done = 0
+        self._generation = getattr(trainer.optimizer, "generation", 0)
         self.graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.static: Dict[Tuple, dict] = {}
         self.pool = None
@@ -111,6 +112,13 @@ class GraphedStep:
     def run(self, x, y, hidden=None):
         """x, y: this iteration's batch on the device.  Returns (loss, acc, hidden)."""
         t, opt = self.t, self.t.optimizer
+        if hasattr(opt, "pre_iteration"):
+            opt.pre_iteration()  # a replay runs no Python of the iteration, so look at the membership here
+        gen = getattr(opt, "generation", 0)
+        if gen != self._generation:  # the process group was re-formed: captured graphs address the old exchange
+            self.graphs.clear()
+            self.static.clear()
+            self.eager_done, self._generation = 0, gen
         if self.eager_done < self.warmup or not self.capturable():
             self.eager_done += 1
             if hidden is not None:
@@ -130,8 +138,6 @@ class GraphedStep:
                     dst.copy_(src.detach(), non_blocking=True)
         if hasattr(opt, "sync_lr"):
             opt.sync_lr()
-        if hasattr(opt, "pre_iteration"):
-            opt.pre_iteration()  # a replay runs no Python of the iteration, so look at the membership here
         g.replay()
         if hasattr(opt, "post_iteration"):
             opt.post_iteration()

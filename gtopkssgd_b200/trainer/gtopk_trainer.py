@@ -52,7 +52,11 @@ def _dump_profiling_norms(optimizer, rank, epoch):
 def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, compression=False,
                 compressor="topk", nwpernode=1, sigma_scale=2.5, pretrain=None, density=0.01, prefix=None,
                 max_iters=None, threshold=None, save_checkpoints=None, check_every=50, cuda_graph=None,
-                prefetch=None, membership_check_every=50):
+                prefetch=None, membership_check_every=50, elastic=False, leave_requested=None):
+    """``elastic``: a rank that gets a departure request (``leave_requested()``
+    turns true, e.g. from a SIGTERM handler) announces it, keeps training up
+    to the agreed iteration and returns; the others re-form a smaller job at
+    that iteration and continue."""
     use_cuda = torch.cuda.is_available()
     rank = dopt.rank()
     if use_cuda:
@@ -83,7 +87,8 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
     optimizer = dopt.DistributedOptimizer(trainer.optimizer, trainer.net.named_parameters(), compression=comp,
                                           is_sparse=compression, err_handler=_error_handler, layerwise_times=None,
                                           sigma_scale=sigma_scale, density=density, norm_clip=None, writer=writer,
-                                          threshold=threshold, membership_check_every=membership_check_every)
+                                          threshold=threshold, membership_check_every=membership_check_every,
+                                          elastic=elastic)
     trainer.update_optimizer(optimizer)
     iters_per_epoch = trainer.get_num_of_training_samples() // (nworkers * batch_size * nsteps_update)
     times, done = [], 0
@@ -122,6 +127,12 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
                 done += 1
                 if max_iters and done >= max_iters:
                     return trainer
+                if elastic:
+                    if leave_requested is not None and leave_requested():
+                        optimizer.request_leave()
+                    if optimizer.should_exit():
+                        logger.info("leaving the job after iteration %d as announced", done)
+                        return trainer
             optimizer.add_train_epoch()
             if settings.PROFILING_NORM:
                 _dump_profiling_norms(optimizer, rank, epoch)
@@ -176,6 +187,9 @@ def build_parser():
     p.add_argument("--save-checkpoints", action="store_true", help="Write a checkpoint at every epoch end")
     p.add_argument("--cuda-graph", action="store_true",
                    help="Capture the whole iteration as a CUDA graph (pays off for launch-bound models)")
+    p.add_argument("--elastic", action="store_true",
+                   help="On SIGTERM a rank announces its departure and leaves at an agreed iteration; "
+                        "the other ranks continue as a smaller job")
     p.add_argument("--prefetch", action="store_true",
                    help="Copy the next batch to the device on a side stream while the current iteration runs")
     p.set_defaults(compression=False)
@@ -210,12 +224,20 @@ def main(argv=None):
     settings.add_file_handler(os.path.join(relative_path, settings.hostname + "-" + str(rank) + ".log"))
     logger.info("Configurations: %s", args)
     logger.info("Interpreter: %s", sys.version)
+    leave = None
+    if args.elastic:
+        import signal
+        import threading
+        asked = threading.Event()
+        signal.signal(signal.SIGTERM, lambda *_: asked.set())
+        leave = asked.is_set
     try:
         robust_ssgd(args.dnn, args.dataset, args.data_dir, args.nworkers, args.lr, args.batch_size,
                     args.nsteps_update, args.max_epochs, args.compression, args.compressor, args.nwpernode,
                     args.sigma_scale, args.pretrain, args.density, prefix, max_iters=args.max_iters,
                     threshold=args.threshold, save_checkpoints=args.save_checkpoints or None,
-                    cuda_graph=args.cuda_graph or None, prefetch=args.prefetch or None)
+                    cuda_graph=args.cuda_graph or None, prefetch=args.prefetch or None, elastic=args.elastic,
+                    leave_requested=leave)
     finally:
         if writer is not None:
             writer.close()

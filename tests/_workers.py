@@ -268,3 +268,47 @@ def gtopk_world3_worker(rank, world):
         msg = str(exc)
     comm.shutdown()
     return msg
+
+
+def elastic_worker(rank, world, compressor, leaver, leave_iter, total_iters):
+    """``leaver`` asks to leave at iteration ``leave_iter``; it trains up to the
+    agreed iteration and returns, the others re-form a smaller job at that
+    iteration and go on to ``total_iters``.  Every rank returns its history."""
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.models import create_net
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("ERROR")
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=60)
+    torch.manual_seed(0)
+    net, _ = create_net(10, "mnistnet")
+    net.eval()
+    comm.broadcast_parameters(net.state_dict(), 0)
+    calls = []
+    opt = torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9)
+    dopt = DistributedOptimizer(opt, net.named_parameters(), compression=compressors[compressor], is_sparse=True,
+                                density=0.01, err_handler=lambda n, r: calls.append((n, r)), wait_limit_ms=30000,
+                                membership_check_every=2, elastic=True)
+    crit = torch.nn.CrossEntropyLoss()
+    hist = []
+    it = 0
+    while it < total_iters:
+        if rank == leaver and it == leave_iter:
+            dopt.request_leave()
+        if dopt.should_exit():
+            break
+        g = torch.Generator().manual_seed(100 * it + rank)
+        x, y = torch.randn(4, 1, 28, 28, generator=g), torch.randint(0, 10, (4,), generator=g)
+        dopt.zero_grad()
+        crit(net(x), y).backward()
+        dopt.step()
+        hist.append((it, comm.size(), comm.rank(), dopt._allreducer.mode))
+        it += 1
+    params = torch.cat([p.detach().flatten() for p in net.parameters()]).clone()
+    out = {"hist": hist, "calls": calls, "params": params, "left_at": dopt.leave_at, "iters": it}
+    dopt.stop()
+    comm.shutdown()
+    return out

@@ -120,3 +120,27 @@ def test_three_workers_allgather_modes(compressor):
 def test_three_workers_gtopk_is_refused():
     out = spawn_ranks(_workers.gtopk_world3_worker, 3, timeout_s=120)
     assert all("power-of-two" in o for o in out), out
+
+
+@pytest.mark.parametrize("world,compressor,leaver", [(4, "topk2", 3), (4, "gtopk", 1), (2, "gtopk", 0)])
+def test_planned_departure_shrinks_the_job(world, compressor, leaver):
+    """A rank announces its departure; every survivor drops it at the same
+    iteration, the process group is re-formed and training continues.  With
+    three workers left gTop-k (power-of-two tree) continues as topk2."""
+    total, leave_iter = 12, 3
+    out = spawn_ranks(_workers.elastic_worker, world, args=(compressor, leaver, leave_iter, total), timeout_s=300)
+    at = out[leaver]["left_at"]
+    assert at == 6                                   # announced at 3, check points every 2: (3 // 2 + 2) * 2
+    assert out[leaver]["iters"] == at                # the leaver took part in iterations 0 .. at-1
+    survivors = [r for r in range(world) if r != leaver]
+    for new_rank, r in enumerate(survivors):
+        o = out[r]
+        assert o["iters"] == total and o["calls"] == [(world - 1, new_rank)]
+        assert [h[1] for h in o["hist"]] == [world] * at + [world - 1] * (total - at)
+        assert o["hist"][-1][2] == new_rank
+        expected_mode = compressor if (world - 1) & (world - 2) == 0 or compressor != "gtopk" else "topk2"
+        assert o["hist"][-1][3] == expected_mode
+        assert torch.isfinite(o["params"]).all()
+    for r in survivors[1:]:                          # the replicas stay identical after the shrink
+        assert torch.equal(out[survivors[0]]["params"], out[r]["params"])
+    assert not torch.equal(out[leaver]["params"], out[survivors[0]]["params"])
