@@ -270,7 +270,7 @@ def gtopk_world3_worker(rank, world):
     return msg
 
 
-def elastic_worker(rank, world, compressor, leaver, leave_iter, total_iters):
+def elastic_worker(rank, world, compressor, leaver, leave_iter, total_iters, device_kind="cpu"):
     """``leaver`` asks to leave at iteration ``leave_iter``; it trains up to the
     agreed iteration and returns, the others re-form a smaller job at that
     iteration and go on to ``total_iters``.  Every rank returns its history."""
@@ -282,9 +282,14 @@ def elastic_worker(rank, world, compressor, leaver, leave_iter, total_iters):
     settings.PIN_DENSITY = True
     settings.logger.setLevel("ERROR")
     torch.set_num_threads(1)
-    comm.init(backend="gloo", timeout_s=60)
+    dev = torch.device("cpu")
+    if device_kind == "cuda":
+        dev = torch.device("cuda", rank)
+        torch.cuda.set_device(dev)
+    comm.init(backend="gloo" if device_kind == "cpu" else "nccl", timeout_s=60)
     torch.manual_seed(0)
     net, _ = create_net(10, "mnistnet")
+    net.to(dev)
     net.eval()
     comm.broadcast_parameters(net.state_dict(), 0)
     calls = []
@@ -301,13 +306,16 @@ def elastic_worker(rank, world, compressor, leaver, leave_iter, total_iters):
         if dopt.should_exit():
             break
         g = torch.Generator().manual_seed(100 * it + rank)
-        x, y = torch.randn(4, 1, 28, 28, generator=g), torch.randint(0, 10, (4,), generator=g)
+        x, y = torch.randn(4, 1, 28, 28, generator=g).to(dev), torch.randint(0, 10, (4,), generator=g).to(dev)
         dopt.zero_grad()
         crit(net(x), y).backward()
         dopt.step()
         hist.append((it, comm.size(), comm.rank(), dopt._allreducer.mode))
         it += 1
-    params = torch.cat([p.detach().flatten() for p in net.parameters()]).clone()
+    if device_kind == "cuda":
+        torch.cuda.synchronize()
+        dopt.check_status()
+    params = torch.cat([p.detach().flatten() for p in net.parameters()]).cpu().clone()
     out = {"hist": hist, "calls": calls, "params": params, "left_at": dopt.leave_at, "iters": it}
     dopt.stop()
     comm.shutdown()

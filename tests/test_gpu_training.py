@@ -136,3 +136,22 @@ def test_prefetched_batches_train_like_host_batches():
             assert all(l == l and l < 1e3 for l in losses)
             first[prefetch] = losses[0]
         assert abs(first[False] - first[True]) < 1e-4, first
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("leaver", [0, 1])
+def test_two_gpu_planned_departure(leaver):
+    """One of two GPU ranks announces its departure (between iterations,
+    nothing in flight); the other closes its peer mappings, leaves the NCCL
+    group and trains on alone from the agreed iteration."""
+    total = 12
+    out = spawn_ranks(_workers.elastic_worker, 2, args=("gtopk", leaver, 3, total, "cuda"), timeout_s=300,
+                      env={"NCCL_NVLS_ENABLE": "0"})
+    other = 1 - leaver
+    at = out[leaver]["left_at"]
+    assert at == 6 and out[leaver]["iters"] == at
+    o = out[other]
+    assert o["iters"] == total and o["calls"] == [(1, 0)]
+    assert [h[1] for h in o["hist"]] == [2] * at + [1] * (total - at)
+    import torch
+    assert torch.isfinite(o["params"]).all() and not torch.equal(o["params"], out[leaver]["params"])
