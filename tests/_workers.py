@@ -320,3 +320,31 @@ def elastic_worker(rank, world, compressor, leaver, leave_iter, total_iters, dev
     dopt.stop()
     comm.shutdown()
     return out
+
+
+def elastic_trainer_worker(rank, world, workdir):
+    """The gTop-k training driver with --elastic semantics: rank 1 is asked to
+    leave after two iterations; rank 0 must finish its ten iterations alone."""
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.trainer import gtopk_trainer
+    os.makedirs(os.path.join(workdir, str(rank)), exist_ok=True)
+    os.chdir(os.path.join(workdir, str(rank)))
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("CRITICAL")
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=60)
+    seen = {"n": 0}
+
+    def asked():
+        seen["n"] += 1
+        return rank == 1 and seen["n"] >= 2
+
+    trainer = gtopk_trainer.robust_ssgd(dnn="mnistnet", dataset="mnist", data_dir="synthetic", nworkers=world, lr=0.01,
+                                        batch_size=4, nsteps_update=1, max_epochs=1, compression=True,
+                                        compressor="gtopk", density=0.01, max_iters=10, membership_check_every=2,
+                                        elastic=True, leave_requested=asked)
+    out = {"iters": trainer.get_train_iter(), "nworkers": trainer.nworkers, "world_now": comm.size(),
+           "loss": trainer.loss}
+    comm.shutdown()
+    return out

@@ -144,3 +144,10 @@ def test_planned_departure_shrinks_the_job(world, compressor, leaver):
     for r in survivors[1:]:                          # the replicas stay identical after the shrink
         assert torch.equal(out[survivors[0]]["params"], out[r]["params"])
     assert not torch.equal(out[leaver]["params"], out[survivors[0]]["params"])
+
+
+def test_elastic_training_driver(tmp_path):
+    out = spawn_ranks(_workers.elastic_trainer_worker, 2, args=(str(tmp_path),), timeout_s=300)
+    assert out[1]["iters"] == 6 and out[1]["nworkers"] == 2          # asked after iteration 1 (train_iter 2): effective at 6
+    assert out[0]["iters"] == 10 and out[0]["nworkers"] == 1 and out[0]["world_now"] == 1
+    assert out[0]["loss"] == out[0]["loss"]
