@@ -19,13 +19,11 @@ oracle.
 """
 from __future__ import annotations
 
-import time
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional
 
 import numpy as np
 import torch
-import torch.distributed as dist
 
 from .. import settings
 from ..ops import exchange as ex

@@ -10,7 +10,7 @@ through this materialising form; it keeps the k pairs sparse end to end.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import numpy as np
 import torch

@@ -12,7 +12,7 @@ raises ``PeerTimeout`` instead of hanging.
 from __future__ import annotations
 
 import datetime
-from typing import Optional, Tuple
+from typing import Tuple
 
 import torch
 import torch.distributed as dist

@@ -12,8 +12,6 @@ device until somebody reads ``trainer.loss``.
 from __future__ import annotations
 
 import argparse
-import logging
-import math
 import os
 import time
 from typing import Optional
@@ -29,7 +27,7 @@ from .. import models, settings
 from ..data import ptb_reader
 from ..data.synthetic import SyntheticAN4, SyntheticImages, SyntheticPTB
 from ..models.lstm import repackage_hidden
-from ..settings import formatter, logger
+from ..settings import logger
 from ..utils import create_path
 
 _support_datasets = ["imagenet", "cifar10", "an4", "ptb", "mnist"]
