@@ -234,6 +234,9 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                 region.close()
                 e.region = None
         new_rank, new_world = comm.reform(survivors)
+        if new_world == 1 and self._watchdog is not None:  # nobody left to wait for
+            self._watchdog.stop()
+            self._watchdog = None
         a.rebuild()
         self._membership = Membership.for_default_group(check_every=self._membership_check_every) \
             if self._membership_check_every else None
