@@ -137,3 +137,16 @@ def test_deepspeech_package_roundtrip_and_description(tmp_path):
     assert info["parameters"] == lm.DeepSpeech.get_param_size(net) and info["epoch"] == 2
     assert info["training"][1] == {"epoch": 2, "loss": 2.0, "wer": 80.0, "cer": 40.0}
     lm.main(["--model-path", str(path)])
+
+
+def test_model_average_of_trainers(tmp_path, monkeypatch):
+    from types import SimpleNamespace
+    from gtopkssgd_b200.trainer.evaluate import model_average
+    nets = []
+    for seed in (0, 1, 2):
+        torch.manual_seed(seed)
+        nets.append(torch.nn.Sequential(torch.nn.Linear(5, 3), torch.nn.BatchNorm1d(3)))
+    want = {k: sum(n.state_dict()[k].float() for n in nets) / 3 for k in nets[0].state_dict()}
+    model_average([SimpleNamespace(net=n) for n in nets])
+    for k, v in nets[0].state_dict().items():
+        assert torch.allclose(v.float(), want[k].to(v.dtype).float(), atol=1e-6), k

@@ -163,3 +163,26 @@ def test_identical_workers_agree_with_local_topk(logp, d, seed):
     assert torch.allclose(gv[order], P * local[0][1][lorder])
     for r in res:  # nothing selected locally was dropped globally: the residual holds only unselected entries
         assert torch.equal(r[gi], torch.zeros(gi.numel()))
+
+
+@hsettings(max_examples=40, deadline=None)
+@given(P=hst.integers(1, 6), d=hst.integers(8, 200), kfrac=hst.floats(0.02, 0.6), seed=hst.integers(0, 10 ** 6))
+def test_allgather_modes_invariants(P, d, kfrac, seed):
+    """'topk' is the dense sum of the P local selections; 'topk2' keeps the k
+    largest magnitudes of that sum (any world size)."""
+    k = max(int(d * kfrac), 1)
+    g = torch.Generator().manual_seed(seed)
+    local = [oracle.compress(torch.randn(d, generator=g), torch.zeros(d), k) for _ in range(P)]
+    dense = oracle.topk_allgather_sum(local, d)
+    ref = torch.zeros(d)
+    for idx, val in local:
+        ref[idx] += val
+    assert torch.allclose(dense, ref, atol=1e-6)
+    gi, gv = oracle.topk2_reselect(local, k)
+    assert gi.numel() <= k and gi.unique().numel() == gi.numel()
+    assert torch.allclose(gv, dense[gi], atol=1e-5)
+    nz = int((dense != 0).sum())
+    if nz > k:  # nothing outside the selection beats anything inside it
+        outside = dense.abs().clone()
+        outside[gi] = 0
+        assert outside.max() <= gv.abs().min() + 1e-6
