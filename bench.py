@@ -195,7 +195,7 @@ def main():
         device_step()
     torch.cuda.synchronize()
     optimizer.check_status()
-    sampler = ClockSampler(gpu_index=device.index or 0)
+    sampler = ClockSampler(gpu_index=device.index or 0, period_ms=100)
     if rank == 0:
         sampler.start()
     native.reset_launch_count()
