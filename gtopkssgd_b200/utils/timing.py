@@ -173,6 +173,13 @@ class ClockSampler:
             self._thread.join(timeout=2)
         sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        if not self._lines:  # the region was shorter than nvidia-smi's start-up: one query right after it
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + _QUERY,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=10)
+                self._lines = [l.strip() for l in out.stdout.splitlines() if l.strip()]
+            except (OSError, subprocess.TimeoutExpired):
+                pass
         for line in self._lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
