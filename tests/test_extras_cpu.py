@@ -150,3 +150,30 @@ def test_model_average_of_trainers(tmp_path, monkeypatch):
     model_average([SimpleNamespace(net=n) for n in nets])
     for k, v in nets[0].state_dict().items():
         assert torch.allclose(v.float(), want[k].to(v.dtype).float(), atol=1e-6), k
+
+
+def test_clock_sampler_parses_and_falls_back(monkeypatch):
+    """Throttle reasons and the median clock come from nvidia-smi's CSV lines;
+    a region too short for a periodic sample gets one query afterwards."""
+    import subprocess
+    from types import SimpleNamespace
+    from gtopkssgd_b200.utils import timing
+    line = "0, 1950, 1965, 640.5, 0x0000000000000004, Not Active, Not Active, Not Active, Active"
+
+    class FakePopen:
+        def __init__(self, *a, **k):
+            self.stdout = iter([])  # the periodic sampler produced nothing
+
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            return 0
+
+    monkeypatch.setattr(subprocess, "Popen", FakePopen)
+    monkeypatch.setattr(subprocess, "run", lambda *a, **k: SimpleNamespace(stdout=line + "\n"))
+    c = timing.ClockSampler(gpu_index=0, period_ms=100)
+    c.start()
+    out = c.stop()
+    assert out["sm_mhz"] == 1950.0 and out["sm_max_mhz"] == 1965.0 and out["samples"] == 1
+    assert out["reasons"] == ["sw_power_cap"] and out["power_w_max"] == 640.5
