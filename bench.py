@@ -12,8 +12,9 @@ with the batch already resident on the GPU; ``e2e`` is the same loop through
 the public trainer API (``DLTrainer.prefetch`` + ``DLTrainer.train_step``): every
 step issues one copy of a batch from pinned host memory (the next step's
 inputs, on a copy stream) and ends with the loss read back to the host.
-``--impl reference`` is the reference arm: it reports why the unmodified
-reference cannot run here.
+``--impl reference`` is the reference arm: the process is replaced by
+``baseline/ref_arm.py``, which runs the unmodified reference on the same
+configuration and prints the same JSON shape.
 """
 from __future__ import annotations
 
@@ -61,12 +62,22 @@ def _emit(real_stdout: int, obj) -> None:
 
 
 def reference_arm(args):
-    reason = ("reference is not installable (no setup.py/pyproject.toml) and imports mpi4py, horovod and "
-              "tensorboardX at module load, none of which exist in this image; it is also Python-2-only "
-              "(dl_trainer.py:490 .next(), allreducer.py:115 range.index)")
-    if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also under torchrun
-        print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
-    return 0
+    """Hands the process over to ``baseline/ref_arm.py``, which drives the unmodified reference under
+    ``baseline/_ref`` (none of this package is imported there).  Same launch, same flags, same JSON shape."""
+    script = os.path.join(ROOT, "baseline", "ref_arm.py")
+    if not os.path.isfile(os.path.join(ROOT, "baseline", "_ref", "allreducer.py")):
+        if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also under torchrun
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref (the copy of the reference tree made "
+                              "by baseline/setup_ref.py) is missing"}), flush=True)
+        return 0
+    argv = [sys.executable, script, "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup),
+            "--model", args.model, "--density", str(args.density), "--compressor", args.compressor]
+    if args.batch_size:
+        argv += ["--batch-size", str(args.batch_size)]
+    if args.skip_e2e:
+        argv.append("--skip-e2e")
+    sys.stdout.flush()
+    os.execv(sys.executable, argv)
 
 
 def main():
