@@ -199,6 +199,23 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                 logger.exception("err_callback raised")
             raise ar.GTopkTimeout(str(exc)) from exc
 
+    def epoch_barrier(self) -> None:
+        """Host-side meeting point at an epoch boundary.  Only rank 0 validates and
+        saves there (dl_trainer.py:606-625 in the reference, where the others then
+        block in MPI without a limit); here every device-side wait of the next
+        exchange is bounded, so the other ranks must not launch it before rank 0 is
+        back.  The barrier runs on the CPU group, whose time limit is that of the
+        job set-up (half an hour by default), not the exchange's.  Heartbeats are
+        renewed on both sides of a second barrier, so nobody looks stale for having
+        waited."""
+        if self._allreducer.size() < 2 or self.capturing:
+            return
+        comm.barrier()
+        m = self._membership
+        if m is not None and m.store is not None:
+            m.beat(self._allreducer.train_iter)
+            comm.barrier()
+
     # -- elastic: planned departures ------------------------------------------------
     def request_leave(self) -> Optional[int]:
         """This rank wants to leave (a pre-emption notice, a drained node).  It

@@ -525,6 +525,10 @@ class DLTrainer:
         self._avg_loss_t = None
         if self.rank == 0 and self.save_checkpoints:
             self.save_checkpoint(self.make_checkpoint(), self.checkpoint_path())
+        # rank 0 alone validated and saved: the others wait for it on the host, not in a bounded device wait
+        meet = getattr(self.optimizer, "epoch_barrier", None)
+        if meet is not None and self.nworkers > 1:
+            meet()
         self.train_epoch += 1
         if self.train_sampler is not None and self.nworkers > 1 and hasattr(self.train_sampler, "set_epoch"):
             self.train_sampler.set_epoch(self.train_epoch)

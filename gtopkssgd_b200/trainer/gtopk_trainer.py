@@ -52,7 +52,8 @@ def _dump_profiling_norms(optimizer, rank, epoch):
 def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, compression=False,
                 compressor="topk", nwpernode=1, sigma_scale=2.5, pretrain=None, density=0.01, prefix=None,
                 max_iters=None, threshold=None, save_checkpoints=None, check_every=50, cuda_graph=None,
-                prefetch=None, membership_check_every=50, elastic=False, leave_requested=None):
+                prefetch=None, membership_check_every=50, elastic=False, leave_requested=None,
+                synthetic_train_size=None):
     """``elastic``: a rank that gets a departure request (``leave_requested()``
     turns true, e.g. from a SIGTERM handler) announces it, keeps training up
     to the agreed iteration and returns; the others re-form a smaller job at
@@ -70,7 +71,8 @@ def robust_ssgd(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update,
     trainer = DLTrainer(rank, nworkers, dist=False, batch_size=batch_size, is_weak_scaling=True,
                         ngpus=1 if use_cuda else 0, data_dir=data_dir, dataset=dataset, dnn=dnn, lr=lr,
                         nworkers=nworkers, prefix=prefix, pretrain=pretrain, tb_writer=writer,
-                        save_checkpoints=save_checkpoints, cuda_graph=cuda_graph)
+                        save_checkpoints=save_checkpoints, cuda_graph=cuda_graph,
+                        synthetic_train_size=synthetic_train_size)
     if prefetch is not None:
         trainer.prefetch_batches = bool(prefetch)
     trainer.set_train_epoch(comm.broadcast_object(trainer.get_train_epoch()))

@@ -348,3 +348,34 @@ def elastic_trainer_worker(rank, world, workdir):
            "loss": trainer.loss}
     comm.shutdown()
     return out
+
+
+def slow_validation_worker(rank, world, workdir):
+    """Epoch boundary with a validation pass on rank 0 that outlasts the exchange's
+    wait limit: the other rank must wait for it on the host and training goes on."""
+    import time
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.trainer import gtopk_trainer
+    from gtopkssgd_b200.trainer.dl_trainer import DLTrainer
+    os.makedirs(os.path.join(workdir, str(rank)), exist_ok=True)
+    os.chdir(os.path.join(workdir, str(rank)))
+    settings.PIN_DENSITY = True
+    settings.WAIT_LIMIT_MS = 1500
+    settings.logger.setLevel("CRITICAL")
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=60)
+    slept = {"n": 0}
+    if rank == 0:
+        def slow_test(self, epoch):
+            slept["n"] += 1
+            time.sleep(4.0)  # far longer than the 1.5 s exchange limit
+            return 0.0
+        DLTrainer.test = slow_test
+    trainer = gtopk_trainer.robust_ssgd(dnn="mnistnet", dataset="mnist", data_dir="synthetic", nworkers=world, lr=0.01,
+                                        batch_size=4, nsteps_update=1, max_epochs=3, compression=True,
+                                        compressor="gtopk", density=0.01, max_iters=None, membership_check_every=1,
+                                        synthetic_train_size=24)
+    out = {"iters": trainer.get_train_iter(), "epoch": trainer.get_train_epoch(), "validations": slept["n"]}
+    comm.shutdown()
+    return out

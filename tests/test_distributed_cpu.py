@@ -151,3 +151,12 @@ def test_elastic_training_driver(tmp_path):
     assert out[1]["iters"] == 6 and out[1]["nworkers"] == 2          # asked after iteration 1 (train_iter 2): effective at 6
     assert out[0]["iters"] == 10 and out[0]["nworkers"] == 1 and out[0]["world_now"] == 1
     assert out[0]["loss"] == out[0]["loss"]
+
+
+def test_validation_longer_than_the_wait_limit_does_not_time_out(tmp_path):
+    """Rank 0 validates for 4 s at every epoch boundary while the exchange's wait limit is 1.5 s: the
+    other rank meets it at a host barrier instead of running into a bounded wait."""
+    out = spawn_ranks(_workers.slow_validation_worker, 2, args=(str(tmp_path),), timeout_s=300)
+    assert out[0]["validations"] >= 2
+    assert out[0]["iters"] == out[1]["iters"] and out[0]["iters"] >= 6
+    assert out[0]["epoch"] == out[1]["epoch"] >= 2
