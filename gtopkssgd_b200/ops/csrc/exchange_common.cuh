@@ -34,8 +34,9 @@ struct K2Rank {
   Pair* ag;
   Pair* gout;
   uint64_t* flags;
-  Ctrl* ctrl;
-  unsigned int* n_global; // device word: number of pairs in gout[parity]
+  Ctrl* ctrl;             // TWO control blocks.  K2 uses block (call & 1) and cleans the other one itself;
+                          // K2t uses block 0, cleared by the host before every launch
+  unsigned int* n_global; // kResWords device words: result of the last call, see kRes* below
   unsigned int* epoch;    // device word: call counter (starts at 1); the kernel reads it at entry and
                           // adds one after its last barrier, so a replayed CUDA graph needs no new argument
   Pair* peer_slots[kMaxPeers];
@@ -43,6 +44,16 @@ struct K2Rank {
   Pair* peer_gout[kMaxPeers];
   uint64_t* peer_flags[kMaxPeers];
 };
+
+// Result words of an exchange (K2Rank::n_global).  kResCount is what the consumer (K3) reads: the
+// number of pairs in gout[parity], 0 after a failed call.  The other three are written once, by
+// the first failing call, and never cleared by a kernel: while kResStatus is non-zero every later
+// call returns at once with an empty result.
+constexpr int kResCount = 0;
+constexpr int kResStatus = 1;
+constexpr int kResWhere = 2;
+constexpr int kResEpoch = 3;
+constexpr int kResWords = 4;
 
 struct ExchangeShared {
   SelectShared sel;

@@ -9,6 +9,9 @@
 //     acc = g*scale + r; entries with |acc| >= tau become candidates (appended to
 //     a bounded list, r <- 0, first radix digit counted), all others r <- acc.
 //     tau is a device-resident prediction from the previous call.
+//     Non-finite entries (+-Inf, NaN) count as the largest magnitudes on both paths,
+//     NaN above Inf, as torch.topk(|acc|) ranks them: they are selected, never left
+//     in the residual.
 // grid barrier
 // Phase 2  normal mode (k <= C <= cap candidates): the first C/1024 CTAs run the
 //     remaining two radix passes over the candidates, compact the k winners,
@@ -23,6 +26,7 @@
 // No host-side clearing: the caller provides two control blocks; call i uses
 // block (i & 1) and zeroes the other one for call i + 1 (i is K1State::n_calls,
 // read on the device, so the launch can be replayed from a CUDA graph).
+#include <atomic>
 #include <cstddef>
 #include "select_common.cuh"
 #include "host_api.h"
@@ -87,6 +91,10 @@ __device__ __forceinline__ void stream_tile(long long v0, long long nvec, long l
                                             Pair* wbuf,
                                             unsigned int& wcnt, Pair* __restrict__ cand, unsigned int cap,
                                             unsigned int* counter, float* __restrict__ r) {
+  // Candidates are decided on the bit pattern of |acc|, which orders like the magnitude for finite
+  // values and puts +-Inf and NaN on top: a non-finite entry is a candidate on this path exactly as it
+  // is the largest key on the exact path (torch.topk(|acc|) in compression.py:43 also ranks NaN first).
+  const uint32_t tau_key = __float_as_uint(tau);
   float4 gv[kK1Vec], rv[kK1Vec];
 #pragma unroll
   for (int u = 0; u < kK1Vec; ++u) {
@@ -110,7 +118,7 @@ __device__ __forceinline__ void stream_tile(long long v0, long long nvec, long l
     a[3] = fmaf(gv[u].w, scale, rv[u].w);
     bool c[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) c[e] = inb && (fabsf(a[e]) >= tau);
+    for (int e = 0; e < 4; ++e) c[e] = inb && (mag_key(a[e]) >= tau_key);
     if (inb) {
       float4 o;
       o.x = c[0] ? 0.f : a[0];
@@ -195,6 +203,7 @@ __device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __re
     }
   }
   // Scalar head and tail (at most 3 + 3 entries), one warp of CTA 0.
+  const uint32_t tau_key = __float_as_uint(tau);
   if (blockIdx.x == 0 && threadIdx.x < 32) {
     const long long nscalar = head + (d - tail0);
     for (long long base = 0; base < nscalar; base += 32) {
@@ -205,7 +214,7 @@ __device__ __forceinline__ void stream_phase(StreamShared& ss, const float* __re
       if (j < nscalar) {
         i = j < head ? j : tail0 + (j - head);
         a = fmaf(g[i], scale, r[i]);
-        c = fabsf(a) >= tau;
+        c = mag_key(a) >= tau_key;
         r[i] = c ? 0.f : a;
       }
       const unsigned int m = __ballot_sync(0xffffffffu, c);
@@ -363,6 +372,7 @@ k1_fused(const float* __restrict__ g, float* __restrict__ r, const float* __rest
     st->kth_mag = t_k;
     st->tau = predict_tau(t_k, 0.f, 0u, k, target_ratio);
   }
+  trace_stamp(ctrl, 5);  // exact mode: CTA 0 collected its share
 }
 
 }  // namespace gtk
@@ -374,17 +384,18 @@ extern "C" unsigned long long gtk_ctrl_bytes(void) { return sizeof(Ctrl); }
 namespace {
 // Co-resident CTAs of k1_fused on the current device (cached).
 int k1_max_grid() {
-  static int cached = 0;
-  if (cached) return cached;
+  static std::atomic<int> cached[64];  // per device: GPUs of one process need not be alike
   const DeviceInfo* di = gtk_device_info();
-  if (!di) return 0;
+  if (!di || di->device < 0 || di->device >= 64) return 0;
+  const int have = cached[di->device].load(std::memory_order_relaxed);
+  if (have) return have;
   int occ = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k1_fused, kK1Threads, 0) != cudaSuccess ||
       occ < 1)
     return 0;
   if (occ > 2) occ = 2;
-  cached = di->sms * occ;
-  return cached;
+  cached[di->device].store(di->sms * occ, std::memory_order_relaxed);
+  return di->sms * occ;
 }
 
 int k1_launch(const float* g, float* r, const float* g_scale, long long d, unsigned int k,
@@ -476,6 +487,10 @@ extern "C" int gtk_k1_select_noalloc(const float* g, float* r, long long d, unsi
   if ((reinterpret_cast<uintptr_t>(g) & 15u) != (reinterpret_cast<uintptr_t>(r) & 15u) ||
       (reinterpret_cast<uintptr_t>(r) & 3u) != 0u)
     return GTK_ERR_ARG;
+  // pairs are stored with one 8-byte access, the count with a 4-byte one
+  if ((reinterpret_cast<uintptr_t>(sel_out) & 7u) != 0u ||
+      (n_sel_out && (reinterpret_cast<uintptr_t>(n_sel_out) & 3u) != 0u))
+    return GTK_ERR_ARG;
   const DeviceInfo* di = gtk_device_info();
   if (!di || di->device < 0 || di->device >= 64) return GTK_ERR_CUDA;
   NoAllocDevice dev;
@@ -509,4 +524,40 @@ extern "C" int gtk_k1_select_noalloc(const float* g, float* r, long long d, unsi
     gtk_count_launch(1);
   }
   return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
+}
+
+// Status of the shared scratch on the current device: out_status_where[0] = status code of the first
+// failure recorded in either control block (0: none; the codes of gtk::Status), [1] = its code
+// location.  With reset != 0 both control blocks and the threshold state are cleared afterwards, which
+// is what brings the entry point back after a failed call (a barrier that ran into its limit leaves
+// its control block marked aborted).  Copies 16 bytes to the host and waits for `stream` only; no
+// allocation.  Returns GTK_ERR_ARG before the first gtk_k1_select_noalloc call on this device.
+extern "C" int gtk_k1_noalloc_status(unsigned int* out_status_where, int reset, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const DeviceInfo* di = gtk_device_info();
+  if (!di || di->device < 0 || di->device >= 64) return GTK_ERR_CUDA;
+  NoAllocDevice dev;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    dev = g_noalloc_dev[di->device];
+  }
+  if (!dev.base) return GTK_ERR_ARG;
+  Ctrl* ctrl_pair = reinterpret_cast<Ctrl*>(dev.base + kNoAllocCtrlOff);
+  unsigned int words[2][2] = {{0u, 0u}, {0u, 0u}};
+  for (int b = 0; b < 2; ++b)
+    if (cudaMemcpyAsync(words[b], &ctrl_pair[b].status, 2 * sizeof(unsigned int), cudaMemcpyDeviceToHost,
+                        stream) != cudaSuccess)
+      return GTK_ERR_CUDA;
+  if (reset) {
+    if (cudaMemsetAsync(ctrl_pair, 0, 2 * sizeof(Ctrl), stream) != cudaSuccess) return GTK_ERR_CUDA;
+    k1_noalloc_reset_state<<<1, 32, 0, stream>>>(reinterpret_cast<K1State*>(dev.base + kNoAllocStateOff));
+    gtk_count_launch(1);
+  }
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return GTK_ERR_CUDA;
+  const int b = words[0][0] ? 0 : 1;
+  if (out_status_where) {
+    out_status_where[0] = words[b][0];
+    out_status_where[1] = words[b][1];
+  }
+  return GTK_OK;
 }

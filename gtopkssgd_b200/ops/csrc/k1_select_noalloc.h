@@ -25,7 +25,14 @@
 // Limits and rules.
 //  * k <= gtk_k1_noalloc_max_k() (16384); larger k is refused with
 //    GTK_ERR_TOO_LARGE and nothing is enqueued.  1 <= d < 2^31.  g and r must be
-//    4-byte aligned and share their offset within a 16-byte line.
+//    4-byte aligned and share their offset within a 16-byte line; sel_out must be
+//    8-byte aligned and n_sel_out 4-byte aligned (GTK_ERR_ARG otherwise: a pair is
+//    stored with one 8-byte access).
+//  * Device-side failures (the grid barrier running into its 2 s limit) are not
+//    visible in the outputs.  gtk_k1_noalloc_status reads the status words out of
+//    the scratch and, on request, clears the scratch so that the next call starts
+//    clean; call it whenever the result matters more than the time of one stream
+//    synchronisation.
 //  * All calls on one device share the one scratch array.  Two calls that overlap
 //    on the GPU (different streams without ordering, or several host threads)
 //    race on it: order them on one stream or with events.
@@ -56,6 +63,12 @@ unsigned long long gtk_k1_noalloc_scratch_bytes(void);
 // pairs written (k, or fewer when d < k).  Enqueues on `stream` and returns.
 int gtk_k1_select_noalloc(const float* g, float* r, long long d, unsigned int k, void* sel_out,
                           unsigned int* n_sel_out, int reset_threshold, void* stream);
+
+// out_status_where: two host words, [0] = status of the first recorded failure
+// (0 none, 2 = barrier limit, 3 = list capacity), [1] = its code location.
+// reset != 0 also clears both control blocks and the predicted threshold.
+// Waits for `stream`; allocates nothing.
+int gtk_k1_noalloc_status(unsigned int* out_status_where, int reset, void* stream);
 
 #ifdef __cplusplus
 }

@@ -16,6 +16,21 @@
 // when all ranks are emulated on one GPU for testing, in which case the launch
 // is cooperative so that all CTAs are co-resident and the flag waits make
 // progress.  gridDim.x CTAs serve each rank and meet in RankBarrier.
+//
+// A merged set is compacted straight to where the next phase reads it: into the
+// partner's receive slot when this rank sends in the next round, into every
+// rank's global-set buffer after the last round (rank 0), into the local work
+// buffer otherwise.  So only round 0 has a separate push, and there is no
+// separate broadcast copy.
+//
+// No host-side clearing: the rank owns two control blocks; call e uses block
+// (e & 1) and zeroes the other one for call e + 1 once its own work is done.
+//
+// Failure: any wait that runs out, any capacity or bounds error makes the call
+// publish an EMPTY global set (n_global = 0, so the consumer applies nothing) and
+// a sticky status in the result words; the call counter is not advanced and every
+// later call returns at once with an empty set until the host has rebuilt the
+// exchange.
 #include <cstddef>
 #include "exchange_common.cuh"
 
@@ -57,9 +72,25 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
   const unsigned int stride = nct * kSelThreads;
   const unsigned int lane0 = cta * kSelThreads + threadIdx.x;  // union index of this thread's trip 0
   const bool single = nct == 1;  // the whole rank is this CTA: histograms never leave shared memory
-  Ctrl* ctrl = R.ctrl;
+  Ctrl* ctrl = R.ctrl + parity;
   int32_t* const map = R.map;
   RankBarrier bar{ctrl, nct, 0u, limit_ns, nullptr, use_cluster != 0};
+  // Leaves an empty result and the sticky status behind; called by every CTA that gives up.
+  auto fail = [&]() {
+    if (threadIdx.x == 0) {
+      atomicExch(&R.n_global[kResCount], 0u);
+      unsigned int st = ld_relaxed_gpu_u32(&ctrl->status);
+      if (st == 0u) st = ST_TIMEOUT_BARRIER;  // left because another CTA of the rank did
+      if (atomicCAS(&R.n_global[kResStatus], 0u, st) == 0u) {
+        R.n_global[kResWhere] = ld_relaxed_gpu_u32(&ctrl->where);
+        R.n_global[kResEpoch] = epoch;
+      }
+    }
+  };
+  if (__ldcg(&R.n_global[kResStatus]) != 0u) {  // an earlier call failed: nothing is exchanged any more
+    if (cta == 0 && threadIdx.x == 0) R.n_global[kResCount] = 0u;
+    return;
+  }
 
   unsigned int n_sel = R.st->n_sel;
   if (n_sel > kcap) n_sel = kcap;
@@ -80,7 +111,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       const unsigned int partner = me - bit;
       Pair* dst = R.peer_slots[partner] + slot_off(parity, r, kcap);
       push_pairs(dst, cur, n_cur, cta, nct);
-      if (!bar.sync(200 + r)) return;
+      if (!bar.sync(200 + r)) { fail(); return; }
       trace_stamp(ctrl, 1 + 8 * r + 6);
       if (cta == 0 && threadIdx.x == 0)
         release_flag(R.peer_flags[partner] + flag_off(parity, r), epoch, n_cur);
@@ -108,8 +139,10 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     }
     unsigned int n_b = 0;
     trace_stamp(ctrl, 1 + 8 * r + 0);
-    if (!cta_wait_flag(sh.ex, R.flags + flag_off(parity, r), epoch, ctrl, limit_ns, 210 + r, &n_b))
+    if (!cta_wait_flag(sh.ex, R.flags + flag_off(parity, r), epoch, ctrl, limit_ns, 210 + r, &n_b)) {
+      fail();
       return;
+    }
     trace_stamp(ctrl, 1 + 8 * r + 1);
     if (n_b > kcap) {
       record_error(ctrl, ST_CAPACITY, 220 + r);
@@ -121,7 +154,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     const unsigned int trips = (n_u + stride - 1) / stride;
     // A and map must be complete: after the copy above that needs a barrier, after a previous
     // round its closing barrier already gave it
-    if (copied && !bar.sync(230 + r)) return;
+    if (copied && !bar.sync(230 + r)) { fail(); return; }
     trace_stamp(ctrl, 1 + 8 * r + 2);
 
     // ---- probe: every thread joins its own B entries against A (sum on shared indices) and
@@ -180,7 +213,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       }
     }
     if (!single) hist0_flush(sh, ctrl->hist[r][0]);
-    if (!bar.sync(240 + r)) return;  // sums and first-digit histogram complete
+    if (!bar.sync(240 + r)) { fail(); return; }  // sums and first-digit histogram complete
     trace_stamp(ctrl, 1 + 8 * r + 3);
 
     // ---- every thread now loads its A entries (with the merged values) next to its B entries
@@ -224,7 +257,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
           atomicAdd(&ss.hist[(mag_key(e.val) >> 10) & 1023u], 1u);
       }
       if (!single) smem_hist_flush(ss, ctrl->hist[r][1], 1024);
-      if (!bar.sync(250 + 10 * r)) return;
+      if (!bar.sync(250 + 10 * r)) { fail(); return; }
       find_digit<1024>(ss, ctrl->hist[r][1], k_rem, single);
       prefix = (prefix << 10) | ss.res_digit;
       k_rem = ss.res_krem;
@@ -240,7 +273,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
         if (e.idx >= 0 && (mag_key(e.val) >> 10) == prefix) atomicAdd(&ss.hist[mag_key(e.val) & 1023u], 1u);
       }
       if (!single) smem_hist_flush(ss, ctrl->hist[r][2], 1024);
-      if (!bar.sync(251 + 10 * r)) return;
+      if (!bar.sync(251 + 10 * r)) { fail(); return; }
       find_digit<1024>(ss, ctrl->hist[r][2], k_rem, single);
       th.key = (prefix << 10) | ss.res_digit;
       th.quota = ss.res_krem;
@@ -248,16 +281,28 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     }
     trace_stamp(ctrl, 1 + 8 * r + 4);
 
-    // ---- compaction of the winners into the other work buffer; the table and the first-digit
-    // histogram of the next round are built on the way
-    Pair* OUT = R.work[cur_buf ^ 1];
-    auto on_placed = [&](Pair e, unsigned int pos) { map[e.idx] = (int32_t)pos; };
+    // ---- compaction of the winners to where the next phase reads them
+    const bool last = r + 1 == rounds;                                  // then me == 0
+    const bool send_next = !last && (me & (4u * bit - 1u)) == 2u * bit;  // sender of round r + 1
+    const bool keep = !last && !send_next;                              // receiver again in round r + 1
+    Pair* OUT;
+    if (last) OUT = R.gout + (size_t)parity * kcap;
+    else if (send_next) OUT = R.peer_slots[me - 2u * bit] + slot_off(parity, r + 1, kcap);
+    else OUT = R.work[cur_buf ^ 1];
+    // keep: the table and (below) the first-digit histogram of the next round are built on the way;
+    // last: the table over the global set serves the residual put-back, and every peer gets its copy
+    auto on_placed = [&](Pair e, unsigned int pos) {
+      if (send_next) return;
+      map[e.idx] = (int32_t)pos;
+      if (last)
+        for (unsigned int q = 1; q < P; ++q) st_pair(R.peer_gout[q] + (size_t)parity * kcap + pos, e);
+    };
     StagedAppender app{&ss, OUT, &ctrl->cursor[r], kcap, ctrl};
     app.begin();
     auto consider = [&](const Pair& e) {
       if (e.idx >= 0 && passes_threshold(mag_key(e.val), th, &ctrl->tie[r])) {
         app.put(e);
-        atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
+        if (keep) atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
       }
     };
 #pragma unroll
@@ -272,46 +317,64 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       app.end_tile(on_placed);
     }
     app.flush(on_placed);
-    if (!single && r + 1 < rounds) hist0_flush(sh, ctrl->hist[r + 1][0]);
-    if (!bar.sync(290 + r)) return;  // OUT and its cursor complete
+    if (!single && keep) hist0_flush(sh, ctrl->hist[r + 1][0]);
+    if (!bar.sync(290 + r)) { fail(); return; }  // OUT and its cursor complete
     trace_stamp(ctrl, 1 + 8 * r + 5);
     n_cur = __ldcg(&ctrl->cursor[r]);
     if (n_cur > kcap) n_cur = kcap;
+    if (send_next) {
+      if (cta == 0 && threadIdx.x == 0)
+        release_flag(R.peer_flags[me - 2u * bit] + flag_off(parity, r + 1), epoch, n_cur);
+      trace_stamp(ctrl, 1 + 8 * (r + 1) + 7);
+      break;  // left the tree
+    }
+    if (last) break;
     cur_buf ^= 1;
     cur = R.work[cur_buf];
   }
 
-  // ---- broadcast of the global set (rank 0 pushes to everyone, itself included)
+  // ---- the global set: rank 0 has just written it into every rank's buffer and only raises the
+  // flags; the others wait for theirs and build the table over it
   Pair* G = R.gout + (size_t)parity * kcap;
   unsigned int n_g = 0;
   if (me == 0u) {
     n_g = n_cur;
-    for (unsigned int q = 0; q < P; ++q) {
-      Pair* dst = (q == 0u ? R.gout : R.peer_gout[q]) + (size_t)parity * kcap;
-      push_pairs(dst, cur, n_cur, cta, nct);
-    }
-    if (!bar.sync(400)) return;
     if (cta == 0 && threadIdx.x < P && threadIdx.x > 0)  // one releasing thread per destination
       release_flag(R.peer_flags[threadIdx.x] + flag_off(parity, kFlagBcast), epoch, n_cur);
+    trace_stamp(ctrl, 40);
+    trace_stamp(ctrl, 41);
   } else {
-    if (!cta_wait_flag(sh.ex, R.flags + flag_off(parity, kFlagBcast), epoch, ctrl, limit_ns, 410, &n_g))
+    if (!cta_wait_flag(sh.ex, R.flags + flag_off(parity, kFlagBcast), epoch, ctrl, limit_ns, 410, &n_g)) {
+      fail();
       return;
+    }
     if (n_g > kcap) {
       record_error(ctrl, ST_CAPACITY, 411);
       n_g = kcap;
     }
+    trace_stamp(ctrl, 40);
+    build_map(G, n_g, map, d, cta, nct, ctrl);
+    if (!bar.sync(420)) { fail(); return; }
+    trace_stamp(ctrl, 41);
   }
   // ---- residual put-back of S_local \ S_global
-  trace_stamp(ctrl, 40);
-  build_map(G, n_g, map, d, cta, nct, ctrl);
-  if (!bar.sync(420)) return;
-  trace_stamp(ctrl, 41);
   put_back(R.sel, n_sel, G, n_g, map, R.resid, d, cta, nct);
-  if (cta == 0 && threadIdx.x == 0) {
-    *R.n_global = n_g;
-    *R.epoch = epoch + 1u;  // safe: all CTAs passed the barrier above, hence read the old value
-  }
   trace_stamp(ctrl, 42);
+  // ---- the other control block, for the next call (nobody waits for this rank any more)
+  {
+    uint4* other = reinterpret_cast<uint4*>(R.ctrl + (parity ^ 1u));
+    const size_t nvec16 = (offsetof(Ctrl, hist) + (size_t)(rounds + 1) * sizeof(((Ctrl*)0)->hist[0])) / 16;
+    for (size_t i = lane0; i < nvec16; i += stride) other[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (!bar.sync(430)) { fail(); return; }  // every CTA is past its last use of the call counter
+  if (cta == 0 && threadIdx.x == 0) {
+    if (aborted(ctrl)) {  // a bounds or capacity error that no wait noticed
+      fail();
+    } else {
+      R.n_global[kResCount] = n_g;
+      *R.epoch = epoch + 1u;
+    }
+  }
 }
 
 }  // namespace gtk
@@ -417,25 +480,19 @@ static bool k2_cluster_fits(unsigned int nranks, unsigned int nctas) {
   return c == 1;
 }
 
-// ranks_dev: device array of nranks_in_launch K2Rank descriptors (1 in production).
-// ctrl_dev[i]: control block of each of those ranks (cleared here).
+// ranks_dev: device array of nranks_in_launch K2Rank descriptors (1 in production).  Nothing is
+// cleared here: the kernel alternates between the two control blocks of each rank.
 // use_cluster: 1 = join the CTAs of a rank into one thread-block cluster (hardware barrier) when
 // nctas is 2, 4, 8 or 16 and the device can hold the clusters; 0 = software barrier.
-extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, unsigned int nranks,
-                               unsigned int rank_base, unsigned int P, unsigned int k,
-                               unsigned int kcap, unsigned int d, unsigned int nctas,
-                               unsigned long long limit_ns, int use_cluster, void* stream_) {
+extern "C" int gtk_k2_exchange(const void* ranks_dev, unsigned int nranks, unsigned int rank_base,
+                               unsigned int P, unsigned int k, unsigned int kcap, unsigned int d,
+                               unsigned int nctas, unsigned long long limit_ns, int use_cluster,
+                               void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (P < 2 || (P & (P - 1)) != 0 || P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
   if (k == 0 || k > kcap || nranks == 0 || nctas == 0) return GTK_ERR_ARG;
   const int maxco = k2_max_coresident((void*)k2_gtopk_exchange);
   if ((int)(nranks * nctas) > maxco) return GTK_ERR_ARG;
-  unsigned int rounds = 0;
-  while ((1u << rounds) < P) ++rounds;
-  // header + trace + one histogram set per round, plus the first-digit histogram of the round after
-  const size_t clear_bytes = offsetof(Ctrl, hist) + (size_t)(rounds + 1) * sizeof(((Ctrl*)0)->hist[0]);
-  for (unsigned int i = 0; i < nranks; ++i)
-    if (cudaMemsetAsync(ctrl_dev[i], 0, clear_bytes, stream) != cudaSuccess) return GTK_ERR_CUDA;
   const K2Rank* ranks = (const K2Rank*)ranks_dev;
   int cluster = (use_cluster && k2_cluster_fits(nranks, nctas)) ? 1 : 0;
   void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &limit_ns, &cluster};
@@ -455,6 +512,10 @@ extern "C" int gtk_k2_exchange(const void* ranks_dev, void* const* ctrl_dev, uns
     cfg.attrs = attr;
     cfg.numAttrs = nranks > 1 ? 2 : 1;  // one cluster is co-scheduled by the hardware anyway
     e = cudaLaunchKernelExC(&cfg, (const void*)k2_gtopk_exchange, args);
+  } else if (nranks * nctas == 1) {
+    // one CTA waits on nobody of its own launch: a plain launch
+    k2_gtopk_exchange<<<dim3(1, 1), dim3(kSelThreads), 0, stream>>>(ranks, rank_base, P, k, kcap, d, limit_ns, 0);
+    e = cudaGetLastError();
   } else {
     e = cudaLaunchCooperativeKernel((void*)k2_gtopk_exchange, dim3(nctas, nranks), dim3(kSelThreads),
                                     args, 0, stream);

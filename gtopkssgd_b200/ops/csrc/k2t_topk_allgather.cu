@@ -29,6 +29,27 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
   RankBarrier bar{ctrl, nct, 0u, limit_ns};
   unsigned int* seg_counts = seg_counts_all + (size_t)blockIdx.y * kMaxPeers;
 
+  // A call that gives up leaves EMPTY results (no segment, no global pair: the consumer applies
+  // nothing) and a sticky status; later calls return at once until the host rebuilds the exchange.
+  auto fail = [&]() {
+    if (threadIdx.x == 0) {
+      atomicExch(&R.n_global[kResCount], 0u);
+      if (cta == 0)
+        for (unsigned int q = 0; q < (unsigned int)kMaxPeers; ++q) seg_counts[q] = 0u;
+      unsigned int st = ld_relaxed_gpu_u32(&ctrl->status);
+      if (st == 0u) st = ST_TIMEOUT_BARRIER;
+      if (atomicCAS(&R.n_global[kResStatus], 0u, st) == 0u) {
+        R.n_global[kResWhere] = ld_relaxed_gpu_u32(&ctrl->where);
+        R.n_global[kResEpoch] = epoch;
+      }
+    }
+  };
+  if (__ldcg(&R.n_global[kResStatus]) != 0u) {
+    if (cta == 0 && threadIdx.x < (unsigned int)kMaxPeers) seg_counts[threadIdx.x] = 0u;
+    if (cta == 0 && threadIdx.x == 0) R.n_global[kResCount] = 0u;
+    return;
+  }
+
   unsigned int n_sel = R.st->n_sel;
   if (n_sel > kcap) n_sel = kcap;
 
@@ -37,7 +58,7 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
     Pair* dst = (q == me ? R.ag : R.peer_ag[q]) + ag_off(parity, me, kcap);
     push_pairs(dst, R.sel, n_sel, cta, nct);
   }
-  if (!bar.sync(500)) return;
+  if (!bar.sync(500)) { fail(); return; }
   if (cta == 0 && threadIdx.x < P && threadIdx.x != me)  // one releasing thread per destination
     release_flag(R.peer_flags[threadIdx.x] + flag_off(parity, kFlagAg0 + me), epoch, n_sel);
   // wait for every source
@@ -46,8 +67,10 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
     unsigned int c = n_sel;
     if (q != me) {
       if (!cta_wait_flag(sh, R.flags + flag_off(parity, kFlagAg0 + q), epoch, ctrl, limit_ns,
-                         510 + q, &c))
+                         510 + q, &c)) {
+        fail();
         return;
+      }
       if (c > kcap) {
         record_error(ctrl, ST_CAPACITY, 530 + q);
         c = kcap;
@@ -57,8 +80,11 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
   }
   if (cta == 0 && threadIdx.x < P) seg_counts[threadIdx.x] = counts[threadIdx.x];
   if (!reselect) {
-    if (!bar.sync(535)) return;  // every CTA has read the epoch word
-    if (cta == 0 && threadIdx.x == 0) *R.epoch = epoch + 1u;
+    if (!bar.sync(535)) { fail(); return; }  // every CTA has read the epoch word
+    if (cta == 0 && threadIdx.x == 0) {
+      if (aborted(ctrl)) fail();
+      else *R.epoch = epoch + 1u;
+    }
     return;
   }
 
@@ -68,7 +94,7 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
   copy_and_map(A, L0, counts[0], R.map, d, cta, nct, ctrl);
   unsigned int n_a = counts[0];
   if (cta == 0 && threadIdx.x == 0) ctrl->n_live = n_a;
-  if (!bar.sync(540)) return;
+  if (!bar.sync(540)) { fail(); return; }
   const unsigned int stride = nct * kSelThreads;
   for (unsigned int q = 1; q < P; ++q) {
     const Pair* B = R.ag + ag_off(parity, q, kcap);
@@ -112,13 +138,13 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
         }
       }
     }
-    if (!bar.sync(560 + q)) return;
+    if (!bar.sync(560 + q)) { fail(); return; }
     n_a = __ldcg(&ctrl->n_live);
     if (n_a > work_cap) n_a = work_cap;
   }
   auto key_at = [&](unsigned int i) -> uint32_t { return mag_key(ld_pair_cg(&A[i]).val); };
   Threshold th;
-  if (!radix_select_kth(sh.sel, bar, cta, nct, n_a, k, ctrl->hist[0], key_at, &th, 580)) return;
+  if (!radix_select_kth(sh.sel, bar, cta, nct, n_a, k, ctrl->hist[0], key_at, &th, 580)) { fail(); return; }
   Pair* G = R.gout + (size_t)parity * kcap;
   int32_t* map = R.map;
   auto on_placed = [&](Pair e, unsigned int pos) { map[e.idx] = (int32_t)pos; };
@@ -134,13 +160,18 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
     app.end_tile(on_placed);
   }
   app.flush(on_placed);
-  if (!bar.sync(590)) return;
+  if (!bar.sync(590)) { fail(); return; }
   unsigned int n_g = __ldcg(&ctrl->cursor[0]);
   if (n_g > kcap) n_g = kcap;
   put_back(R.sel, n_sel, G, n_g, R.map, R.resid, d, cta, nct);
+  if (!bar.sync(595)) { fail(); return; }
   if (cta == 0 && threadIdx.x == 0) {
-    *R.n_global = n_g;
-    *R.epoch = epoch + 1u;
+    if (aborted(ctrl)) {
+      fail();
+    } else {
+      R.n_global[kResCount] = n_g;
+      *R.epoch = epoch + 1u;
+    }
   }
 }
 

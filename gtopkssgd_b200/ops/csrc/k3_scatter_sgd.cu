@@ -155,6 +155,37 @@ k3_scatter_dense(float* __restrict__ g, const Pair* __restrict__ pairs,
   }
 }
 
+// Momentum correction (distributed_optimizer.py:81-88 in the reference, off by default there): the
+// velocity, not the raw gradient, is what gets sparsified.  v = m*v + g; g = v, over a whole merged
+// group in one pass (the reference does it per parameter tensor inside the gradient hook).
+__global__ void __launch_bounds__(kK3Threads, 2)
+k3_momentum_correct(float* __restrict__ v, float* __restrict__ g, float m, long long d) {
+  const unsigned int mis = (unsigned int)((reinterpret_cast<uintptr_t>(g) >> 2) & 3u);
+  long long head = mis ? (4 - mis) : 0;
+  if (head > d) head = d;
+  const long long nvec = (d - head) >> 2;
+  const long long tail0 = head + (nvec << 2);
+  float4* v4 = reinterpret_cast<float4*>(v + head);
+  float4* g4 = reinterpret_cast<float4*>(g + head);
+  const long long stride = (long long)gridDim.x * kK3Threads;
+  for (long long i = (long long)blockIdx.x * kK3Threads + threadIdx.x; i < nvec; i += stride) {
+    float4 a = v4[i];
+    const float4 b = g4[i];
+    a.x = fmaf(m, a.x, b.x); a.y = fmaf(m, a.y, b.y); a.z = fmaf(m, a.z, b.z); a.w = fmaf(m, a.w, b.w);
+    v4[i] = a;
+    g4[i] = a;
+  }
+  if (blockIdx.x == 0) {
+    const long long nscalar = head + (d - tail0);
+    for (long long j = threadIdx.x; j < nscalar; j += kK3Threads) {
+      const long long i = j < head ? j : tail0 + (j - head);
+      const float a = fmaf(m, v[i], g[i]);
+      v[i] = a;
+      g[i] = a;
+    }
+  }
+}
+
 }  // namespace gtk
 
 using namespace gtk;
@@ -220,6 +251,15 @@ extern "C" int gtk_k3_scatter_dense(float* g, const void* pairs, const unsigned 
   k3_scatter_dense<<<blocks, 256, 0, stream>>>(g, (const Pair*)pairs, counts, nseg, seg_stride,
                                                scale, (unsigned int)d, use_atomics, parity_word,
                                                parity_stride);
+  gtk_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
+}
+
+extern "C" int gtk_k3_momentum_correct(float* v, float* g, float momentum, long long d, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (d <= 0 || !v || !g) return GTK_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(v) & 15u) != (reinterpret_cast<uintptr_t>(g) & 15u)) return GTK_ERR_ARG;
+  k3_momentum_correct<<<dense_grid(d), kK3Threads, 0, stream>>>(v, g, momentum, d);
   gtk_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? GTK_OK : GTK_ERR_CUDA;
 }

@@ -22,6 +22,7 @@ from . import lib as _lib
 from .select import TopkSelector, current_stream_handle
 
 MAX_PEERS = 16
+RES_COUNT, RES_STATUS, RES_WHERE, RES_EPOCH, RES_WORDS = 0, 1, 2, 3, 4   # K2Rank::n_global words (exchange_common.cuh)
 GUARD_BYTES = 256      # canary band before and after every symmetric region
 GUARD_PATTERN = 0xA5
 
@@ -124,8 +125,17 @@ class ExchangeRank:
         self.work0 = torch.empty((self.work_cap, 2), dtype=torch.int32, device=dev)
         self.work1 = torch.empty((self.kcap, 2), dtype=torch.int32, device=dev)
         self.map = torch.zeros(self.numel, dtype=torch.int32, device=dev)
-        self.ctrl = torch.zeros(int(L.gtk_ctrl_bytes()) // 4, dtype=torch.int32, device=dev)
-        self.n_global = torch.zeros(1, dtype=torch.int32, device=dev)
+        # two control blocks: the gTop-k kernel alternates between them and cleans the idle one itself
+        self.ctrl_words = int(L.gtk_ctrl_bytes()) // 4
+        self.ctrl = torch.zeros(2 * self.ctrl_words, dtype=torch.int32, device=dev)
+        # result words of the last exchange: [count of global pairs, sticky status, where, failing call]
+        self.result_words = torch.zeros(RES_WORDS, dtype=torch.int32, device=dev)
+        self.n_global = self.result_words[0:1]
+        # host mirror of the result words, refreshed by an asynchronous copy behind every exchange, so
+        # that the host can look at the status before each iteration without synchronising
+        self.result_host = torch.zeros(RES_WORDS, dtype=torch.int32)
+        if dev.type == "cuda":
+            self.result_host = self.result_host.pin_memory()
         self.seg_counts = torch.zeros(MAX_PEERS, dtype=torch.int32, device=dev)
         # call counter of this rank's exchanges: the kernel reads it at entry (flag epoch, slot parity)
         # and adds one at exit, so launches carry no per-call argument and can be replayed from a graph
@@ -151,8 +161,41 @@ class ExchangeRank:
         return self.region.local_ptr + self.layout[1] + parity * MAX_PEERS * self.kcap * 8
 
     def status(self) -> Tuple[int, int]:
-        c = self.ctrl[:8].cpu()
-        return int(c[_lib.CTRL_STATUS]), int(c[_lib.CTRL_WHERE])
+        """(status, code location) of the first failure, (0, 0) if none (synchronises)."""
+        w = self.result_words.cpu()
+        if int(w[RES_STATUS]) != 0:
+            return int(w[RES_STATUS]), int(w[RES_WHERE])
+        for b in range(2):
+            c = self.ctrl[b * self.ctrl_words:b * self.ctrl_words + 8].cpu()
+            if int(c[_lib.CTRL_STATUS]) != 0:
+                return int(c[_lib.CTRL_STATUS]), int(c[_lib.CTRL_WHERE])
+        return 0, 0
+
+    def mirror_status(self) -> None:
+        """Enqueue the copy of the result words to pinned host memory on the current stream."""
+        self.result_host.copy_(self.result_words, non_blocking=True)
+
+    def failed_on_host_mirror(self) -> Tuple[int, int]:
+        """What the last completed mirror copy showed; never synchronises."""
+        return int(self.result_host[RES_STATUS]), int(self.result_host[RES_WHERE])
+
+    def clear_failure(self) -> None:
+        """Forget a recorded failure so that the exchange runs again.  Every rank of
+        the job has to do this at the same point, with nothing in flight (the call
+        counter, which stamps the flags, was not advanced by the failed call)."""
+        self.result_words.zero_()
+        self.result_host.zero_()
+        self.ctrl.zero_()
+
+    def last_ctrl(self) -> torch.Tensor:
+        """Control block that the last completed gTop-k call used (synchronises)."""
+        b = (int(self.epoch.item()) - 1) & 1
+        return self.ctrl[b * self.ctrl_words:(b + 1) * self.ctrl_words]
+
+    def trace(self) -> dict:
+        """Phase stamps of the last completed gTop-k call, decoded (``decode_k2_trace``)."""
+        world = self.world
+        return decode_k2_trace(_lib.read_trace(self.last_ctrl()), self.rank, world)
 
     def last_parity(self) -> int:
         """Parity of the slot set the last completed exchange wrote (synchronises)."""
@@ -205,8 +248,7 @@ def launch_gtopk(ranks: Sequence[ExchangeRank], desc: torch.Tensor, rank_base: i
     r0 = ranks[0]
     if nctas is None:
         nctas = default_nctas(k, len(ranks))
-    ctrls = (C.c_void_p * len(ranks))(*[C.c_void_p(r.ctrl.data_ptr()) for r in ranks])
-    code = L.gtk_k2_exchange(desc.data_ptr(), ctrls, len(ranks), rank_base, world, k, r0.kcap, r0.numel,
+    code = L.gtk_k2_exchange(desc.data_ptr(), len(ranks), rank_base, world, k, r0.kcap, r0.numel,
                              nctas, int(limit_ms * 1e6), int(use_cluster), current_stream_handle(r0.resid.device))
     _lib.check(code, "gtk_k2_exchange")
 
@@ -226,6 +268,42 @@ def launch_allgather(ranks: Sequence[ExchangeRank], desc: torch.Tensor, seg_coun
                                r0.numel, int(reselect), seg_counts.data_ptr(), nctas,
                                int(limit_ms * 1e6), current_stream_handle(r0.resid.device))
     _lib.check(code, "gtk_k2t_allgather")
+
+
+def decode_k2_trace(tr: dict, rank: int, world: int) -> dict:
+    """Turns the %globaltimer stamps that CTA 0 of a rank leaves in its control block
+    (slot 0: start; 1 + 8r + j for tree round r: j = 0 before / 1 after the wait for the
+    partner's flag, 2 table complete, 3 join done, 4 threshold known, 5 compaction done,
+    6 pushed (round-0 sender), 7 flag raised; 40 global set here, 41 its table built,
+    42 put-back done) into microseconds: ``total``, ``wait`` (time inside flag waits:
+    partner or root not there yet), ``work`` = total - wait, and per-phase entries."""
+    if 42 not in tr:
+        return {"complete": False}
+    us = lambda a, b: (tr[b] - tr[a]) / 1e3 if a in tr and b in tr else 0.0
+    rounds = max(world.bit_length() - 1, 0)
+    out = {"complete": True, "total": tr[42] / 1e3, "wait": 0.0, "rounds": []}
+    last = 0
+    for r in range(rounds):
+        b = 1 + 8 * r
+        row = {}
+        if b + 1 in tr:  # receiver of round r
+            row = {"role": "recv", "wait": us(b, b + 1), "table": us(b + 1, b + 2), "join": us(b + 2, b + 3),
+                   "select": us(b + 3, b + 4), "compact": us(b + 4, b + 5)}
+            out["wait"] += row["wait"]
+            last = b + 5
+        if b + 7 in tr:  # sent in round r (round 0: after a push; later: straight from the compaction)
+            row = dict(row, sent=True) if row else {"role": "send", "push": us(last, b + 6) if b + 6 in tr else 0.0,
+                                                     "flag": us(b + 6, b + 7) if b + 6 in tr else 0.0}
+            last = b + 7
+        out["rounds"].append(row)
+    if rank != 0:
+        w = us(last, 40)
+        out["wait"] += w
+        out["bcast_wait"] = w
+    out["table_g"] = us(40, 41)
+    out["put_back"] = us(41, 42)
+    out["work"] = out["total"] - out["wait"]
+    return out
 
 
 def region_bytes(kcap: int, with_allgather: bool) -> int:

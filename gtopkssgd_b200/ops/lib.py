@@ -65,7 +65,7 @@ def _declare(lib):
     lib.gtk_symm_layout.restype = None
     lib.gtk_k2rank_fill.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, i32, u32, C.POINTER(vp)]
     lib.gtk_k2rank_fill.restype = i32
-    lib.gtk_k2_exchange.argtypes = [vp, C.POINTER(vp), u32, u32, u32, u32, u32, u32, u32, u64, i32, vp]
+    lib.gtk_k2_exchange.argtypes = [vp, u32, u32, u32, u32, u32, u32, u32, u64, i32, vp]
     lib.gtk_k2_exchange.restype = i32
     lib.gtk_k2t_allgather.argtypes = [vp, C.POINTER(vp), u32, u32, u32, u32, u32, u32, u32, i32, vp, u32, u64, vp]
     lib.gtk_k2t_allgather.restype = i32
@@ -74,6 +74,8 @@ def _declare(lib):
     lib.gtk_k3_sparse.argtypes = [vp, vp, vp, vp, u32, u32, vp, f32, u32, f32, vp, f32, f32, f32, i32, i32, i32, vp,
                                   vp, u32, vp]
     lib.gtk_k3_sparse.restype = i32
+    lib.gtk_k3_momentum_correct.argtypes = [vp, vp, f32, i64, vp]
+    lib.gtk_k3_momentum_correct.restype = i32
     lib.gtk_k3_scatter_dense.argtypes = [vp, vp, vp, u32, u32, f32, i64, i32, vp, u32, vp]
     lib.gtk_k3_scatter_dense.restype = i32
     lib.gtk_k4_sumsq_dense.argtypes = [vp, i64, vp, vp]

@@ -83,6 +83,17 @@ class TopkSelector:
                 return int(c[_lib.CTRL_STATUS]), int(c[_lib.CTRL_WHERE])
         return (0, 0)
 
+    def trace(self) -> dict:
+        """Device-side phase stamps of the last select, in nanoseconds since its
+        start: slot 1 = CTA 0 finished its share of the stream pass, 2 = every CTA
+        did (grid barrier passed), 3 = k-th magnitude known, 4 = winners compacted
+        (3 and 4 only on the predicted-threshold path).  Synchronises."""
+        if not self.is_cuda:
+            return {}
+        calls = int(self.state[5].item())
+        b = (calls - 1) & 1
+        return _lib.read_trace(self.ctrl[b * self.ctrl_words:(b + 1) * self.ctrl_words])
+
     def reset(self) -> None:
         """Back to the initial state (after a reported failure)."""
         if self.is_cuda:

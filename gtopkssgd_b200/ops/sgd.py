@@ -116,3 +116,17 @@ def _scratch_word(device: torch.device) -> torch.Tensor:
     if key not in _scratch:
         _scratch[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _scratch[key]
+
+
+def momentum_correct(v: torch.Tensor, g: torch.Tensor, momentum: float) -> None:
+    """v = momentum * v + g; g = v, in place over flat buffers (one launch).
+    The reference applies this per parameter in its gradient hook when
+    ``momentum_correction`` is set (distributed_optimizer.py:81-88)."""
+    if g.device.type != "cuda":
+        v.mul_(momentum).add_(g)
+        g.copy_(v)
+        return
+    L = _lib.lib()
+    code = L.gtk_k3_momentum_correct(v.data_ptr(), g.data_ptr(), C.c_float(momentum), g.numel(),
+                                     current_stream_handle(g.device))
+    _lib.check(code, "gtk_k3_momentum_correct")

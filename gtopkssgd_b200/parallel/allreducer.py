@@ -90,6 +90,7 @@ class GroupEngine:
             raise ValueError("merged group %d holds %d elements; the sparse pairs carry int32 indices, so a group must "
                              "stay below 2^31 elements: lower the merge threshold" % (g.index, self.numel))
         self.last_k = 0
+        self.select_done = None
         self.result: Optional[SparseResult] = None
         self.dense_ready = False
         dev = fb.device
@@ -130,6 +131,11 @@ class GroupEngine:
         t = o.timers
         t.start(self.g.key, "compression")
         self.selector.select(self.grad, self.resid, k, g_scale=g_scale)
+        if self.is_cuda:
+            # the dense part of the update streams the same HBM as the select: it is ordered behind this
+            # event, so the select has the bandwidth to itself and the dense part overlaps the exchange
+            self.select_done = torch.cuda.Event()
+            self.select_done.record()
         t.stop(self.g.key, "compression")
         t.start(self.g.key, "allreduce")
         if world == 1:
@@ -149,6 +155,7 @@ class GroupEngine:
                 else:
                     self.result = SparseResult(self.gout, rc.n_global, 1, self.max_k, False, 1.0 / world,
                                                rc.epoch, rc.parity_stride)
+            rc.mirror_status()  # 16 bytes to pinned host memory, read by poll_failure() before the next iteration
         else:
             self._reduce_host(k, world, mode)
         t.stop(self.g.key, "allreduce")
@@ -188,6 +195,25 @@ class GroupEngine:
             o.report_failure(str(exc))
             raise GTopkTimeout(str(exc)) from exc
 
+    def poll_failure(self) -> None:
+        """Look at the host mirror of the exchange's result words (refreshed behind
+        every exchange, at most an iteration old) without synchronising.  A failed
+        exchange has applied nothing (its global set is empty) and every later one
+        returns at once, so raising here, before the next iteration is launched,
+        loses no more than the iterations in flight."""
+        rc = getattr(self, "rank_ctx", None)
+        if rc is None:
+            return
+        status, where = rc.failed_on_host_mirror()
+        if status != 0:
+            self._raise_status(status, where)
+
+    def _raise_status(self, status: int, where: int) -> None:
+        from ..ops.lib import STATUS_NAMES
+        msg = "group %s: %s (code location %d)" % (self.g.key[:40], STATUS_NAMES.get(status, status), where)
+        self.owner.report_failure(msg)
+        raise GTopkTimeout(msg)
+
     def check_status(self) -> None:
         """Read the device status words of the last exchange (synchronises the
         stream it ran on).  Raises GTopkTimeout after telling err_callback."""
@@ -195,10 +221,7 @@ class GroupEngine:
             return
         status, where = self.rank_ctx.status()
         if status != 0:
-            from ..ops.lib import STATUS_NAMES
-            msg = "group %s: %s (code location %d)" % (self.g.key[:40], STATUS_NAMES.get(status, status), where)
-            self.owner.report_failure(msg)
-            raise GTopkTimeout(msg)
+            self._raise_status(status, where)
         region = getattr(self, "region", None)
         if region is not None and not region.guards_intact():
             raise RuntimeError("group %s: a store landed outside the exchange slots (guard band of the "
@@ -317,6 +340,10 @@ class AllReducer:
         for e in self.engines:
             e.check_status()
 
+    def poll_failure(self) -> None:
+        for e in self.engines:
+            e.poll_failure()
+
     def report_failure(self, msg: str) -> None:
         """A peer is gone: tell the trainer (it may shrink the world and
         re-shard its data) once per failure."""
@@ -396,6 +423,7 @@ class AllReducer:
             return
         self._running = True
         arrived = [0] * len(self.engines)
+        reduced = 0  # groups completed in the current iteration
         while self._running:
             name = self._msg_queue.get()
             if name == MESSAGE.STOP:
@@ -405,9 +433,14 @@ class AllReducer:
             if arrived[gi] == len(self._groups[gi]):
                 arrived[gi] = 0
                 self.reduce_group(gi)
-                if not any(arrived) and self._msg_queue2 is not None:
-                    self.reset()
-                    self._msg_queue2.put("DONE")
+                reduced += 1
+                # names arrive in backward order, so the last group completes first: "DONE" is due only
+                # when all of them have been reduced (allreducer.py:594-597)
+                if reduced == len(self.engines):
+                    reduced = 0
+                    if self._msg_queue2 is not None:
+                        self.reset()
+                        self._msg_queue2.put("DONE")
 
     def rebuild(self) -> None:
         """The process group changed (a smaller world after a planned

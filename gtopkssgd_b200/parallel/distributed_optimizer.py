@@ -30,7 +30,7 @@ import torch
 
 from .. import settings
 from ..ops.clip import ClipNorm
-from ..ops.sgd import SgdHyper, scatter_dense, sgd_dense, sgd_sparse
+from ..ops.sgd import SgdHyper, momentum_correct, scatter_dense, sgd_dense, sgd_sparse
 from ..settings import logger
 from . import allreducer as ar
 from . import comm
@@ -145,20 +145,21 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                 return
             if p.grad is None or p.grad.data_ptr() != self._flat.grad.data_ptr() + 4 * slot.offset:
                 self._flat.ensure_views()
-            if self.momentum_correction:
-                self._apply_momentum_correction(slot)
             self._arrived[gi] += 1
             if self._arrived[gi] == self._expected[gi] and not self._launched[gi]:
                 self._launch_group(gi)
         return hook
 
-    def _apply_momentum_correction(self, slot):
+    def _apply_momentum_correction(self, gi: int) -> None:
         """Optional (off by default, distributed_optimizer.py:81-88): the
-        velocity, not the raw gradient, is what gets sparsified."""
-        buf = self._flat.momentum_view(slot.name)
-        g = self._flat.grad_view(slot.name)
-        buf.mul_(0.9).add_(g)
-        g.copy_(buf)
+        velocity, not the raw gradient, is what gets sparsified.  One launch
+        over the merged group once its last gradient is there (the reference
+        updates parameter by parameter inside the hook; the result is the same).
+        The factor is the wrapped optimizer's momentum, 0.9 if it has none."""
+        eng = self._allreducer.engines[gi]
+        fb = self._flat
+        m = float(self.param_groups[0].get("momentum", 0.0)) or 0.9
+        momentum_correct(fb.group_slice(fb.momentum, eng.g), eng.grad, m)
 
     def _launch_group(self, gi: int) -> None:
         self._launched[gi] = True
@@ -167,8 +168,12 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             ev.record()
             self._comm_stream.wait_event(ev)
             with torch.cuda.stream(self._comm_stream):
+                if self.momentum_correction:
+                    self._apply_momentum_correction(gi)
                 self._allreducer.reduce_group(gi)
         else:
+            if self.momentum_correction:
+                self._apply_momentum_correction(gi)
             self._allreducer.reduce_group(gi)
 
     # -- public API ---------------------------------------------------------------
@@ -181,6 +186,8 @@ class _DistributedOptimizer(torch.optim.Optimizer):
             msg, self._stalled = self._stalled, None
             self._allreducer.report_failure(msg)
             raise ar.GTopkTimeout(msg)
+        if not self.capturing:
+            self._allreducer.poll_failure()  # status of the exchanges already completed; no synchronisation
         m = self._membership
         if m is None or self.capturing:
             return
@@ -362,6 +369,8 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                 sgd_dense(p, buf, h, first, g=eng.grad, scale=scale, coef=self._post_coef, lr_dev=lr_dev)
         else:
             for eng in a.engines:
+                if eng.select_done is not None and self._is_cuda:
+                    torch.cuda.current_stream().wait_event(eng.select_done)  # select first, then dense || exchange
                 p, buf = bufs(eng)
                 sgd_dense(p, buf, h, first, lr_dev=lr_dev)
             self.synchronize()

@@ -379,3 +379,37 @@ def slow_validation_worker(rank, world, workdir):
     out = {"iters": trainer.get_train_iter(), "epoch": trainer.get_train_epoch(), "validations": slept["n"]}
     comm.shutdown()
     return out
+
+
+def selfcheck_worker(rank, world, compressor):
+    """Two training iterations on gloo ranks, then the checked exchange that bench.py
+    runs at its end on real GPUs."""
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.models import create_net
+    from gtopkssgd_b200.parallel import comm
+    from gtopkssgd_b200.parallel.compression import compressors
+    from gtopkssgd_b200.parallel.distributed_optimizer import DistributedOptimizer
+    from gtopkssgd_b200.parallel.selfcheck import exchange_selfcheck
+    settings.PIN_DENSITY = True
+    settings.logger.setLevel("ERROR")
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=60)
+    torch.manual_seed(0)
+    net, _ = create_net(10, "mnistnet")
+    comm.broadcast_parameters(net.state_dict(), 0)
+    opt = torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9)
+    dopt = DistributedOptimizer(opt, net.named_parameters(), compression=compressors[compressor], is_sparse=True,
+                                density=0.01, wait_limit_ms=30000, threshold=8000)
+    crit = torch.nn.CrossEntropyLoss()
+    for it in range(2):
+        g = torch.Generator().manual_seed(100 * it + rank)
+        x, y = torch.randn(4, 1, 28, 28, generator=g), torch.randint(0, 10, (4,), generator=g)
+        dopt.zero_grad()
+        crit(net(x), y).backward()
+        dopt.step()
+    dopt.zero_grad()
+    crit(net(x), y).backward()  # leaves a fresh local gradient in the buffers, already reduced once by the hooks
+    out = exchange_selfcheck(dopt)
+    dopt.stop()
+    comm.shutdown()
+    return out

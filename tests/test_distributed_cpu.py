@@ -160,3 +160,13 @@ def test_validation_longer_than_the_wait_limit_does_not_time_out(tmp_path):
     assert out[0]["validations"] >= 2
     assert out[0]["iters"] == out[1]["iters"] and out[0]["iters"] >= 6
     assert out[0]["epoch"] == out[1]["epoch"] >= 2
+
+
+@pytest.mark.parametrize("world,compressor", [(2, "gtopk"), (4, "gtopk"), (3, "topk2"), (2, "topk")])
+def test_exchange_selfcheck_on_gloo_ranks(world, compressor):
+    """The checked exchange that the benchmark runs on real GPUs, here over the gloo fallback."""
+    out = spawn_ranks(_workers.selfcheck_worker, world, args=(compressor,), timeout_s=300)
+    for o in out:
+        assert o["ok"], o
+        assert len(o["groups"]) >= 2 and o["max_rel_err"] <= 1e-5
+        assert all(g["index_sets_equal"] and g["residual_ok_all_ranks"] and g["select_ok_all_ranks"] for g in o["groups"])

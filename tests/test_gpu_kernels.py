@@ -110,6 +110,47 @@ def test_k1_unaligned_views_and_scale():
         assert float(big_r[:off].abs().sum()) == 0.0 and float(big_r[off + d:].abs().sum()) == 0.0
 
 
+def test_k1_non_finite_entries_are_selected_on_both_paths():
+    """NaN and +-Inf count as the largest magnitudes (NaN above Inf), as
+    torch.topk(|acc|) of the reference ranks them (compression.py:43): they are
+    selected and leave the residual on the exact path (first call) and on the
+    predicted-threshold path (later calls) alike."""
+    torch.manual_seed(9)
+    d, k = 300_000, 300
+    sel = _selector(d, k)
+    r = torch.zeros(d, device=DEV)
+    planted = {0: [(17, float("nan")), (d - 1, float("inf"))],              # call 0: exact path
+               2: [(4096, float("-inf")), (123_457, float("nan")), (3, float("nan"))]}  # call 2: predicted threshold
+    for it in range(4):
+        g = torch.randn(d, device=DEV)
+        for j, v in planted.get(it, []):
+            g[j] = v
+        r_before = r.clone()
+        sel.select(g, r, k)
+        idx, val = sel.pairs()
+        assert sel.status() == (0, 0) and idx.numel() == k
+        got = dict(zip(idx.cpu().tolist(), val.cpu().tolist()))
+        assert len(got) == k
+        bad = planted.get(it, [])
+        for j, v in bad:
+            assert j in got, "call %d: non-finite entry %d not selected" % (it, j)
+            assert (math.isnan(v) and math.isnan(got[j])) or got[j] == v
+            assert float(r[j]) == 0.0
+        # the finite rest: the k - len(bad) largest finite magnitudes, residual = acc off the selection
+        acc = (g + r_before).cpu()
+        finite = acc.clone()
+        for j, _ in bad:
+            finite[j] = 0.0
+        top = set(torch.topk(finite.abs(), k - len(bad)).indices.tolist())
+        assert set(got) - {j for j, _ in bad} == top
+        keep = torch.ones(d, dtype=torch.bool)
+        keep[list(got)] = False
+        assert torch.equal(r.cpu()[keep], acc[keep])
+        assert torch.isfinite(r).all()
+        if it == 2:
+            assert sel.stats()["fallback"] == 0, "call 2 was meant to run on the predicted threshold"
+
+
 def test_k1_scale_jump_and_ties():
     """A 5x scale jump overflows or starves the candidate list: the exact path
     must take over; repeated values must still give exactly k entries."""
@@ -350,10 +391,23 @@ def test_k2_bounded_wait_reports_timeout():
     torch.cuda.synchronize()
     status, where = ranks[0].status()
     assert status == 1 and 210 <= where < 220
-    # the device is still healthy and the next (complete) exchange works
+    assert int(ranks[0].n_global.item()) == 0  # an empty global set: the consumer applies nothing
+    assert int(ranks[0].epoch.item()) == 1     # the aborted call did not advance the counter
+    # a failed exchange stays failed: the next call returns at once (no second wait), still empty
+    import time
+    ranks[0].n_global.fill_(123)
+    t0 = time.time()
+    ex.launch_gtopk(ranks[:1], ranks[0].desc, 0, 2, k, nctas=2, limit_ms=5000)
+    ranks[0].mirror_status()
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 2.0
+    assert int(ranks[0].n_global.item()) == 0 and ranks[0].status()[0] == 1
+    assert ranks[0].failed_on_host_mirror()[0] == 1  # what the host sees without synchronising
+    # the host clears the failure (all ranks together); the device is healthy and a complete exchange works
+    ranks[0].clear_failure()
+    assert ranks[0].status() == (0, 0)
     for r in ranks:
         r.selector.select(torch.randn(d, device=DEV), r.resid, k)
-    assert int(ranks[0].epoch.item()) == 1  # the aborted call did not advance the counter
     ex.launch_gtopk(ranks, desc, 0, 2, k, nctas=1, limit_ms=2000)
     torch.cuda.synchronize()
     assert all(r.status() == (0, 0) for r in ranks)
