@@ -3,7 +3,12 @@
 --models  prints the alpha-beta predictions for dense / Top-k / gTop-k and the
           published scaling efficiencies;
 --log     summarises a trainer log (epoch losses, validation metric, mean speed,
-          communication profile)."""
+          communication profile);
+--p2p     fits time = alpha + beta * size to a point-to-point probe log;
+--allreduce-log FILE --workers N   compares a measured all-reduce log with the
+          ring model (mean relative error);
+--layers  per-layer log: message-size statistics and the WFBP / single /
+          merged timeline totals."""
 from __future__ import annotations
 
 import argparse
@@ -18,8 +23,28 @@ def main(argv=None):
     ap.add_argument("--models", action="store_true")
     ap.add_argument("--m", type=int, default=25 * 1024 * 1024)
     ap.add_argument("--rho", type=float, default=0.001)
+    ap.add_argument("--p2p", type=str, default=None)
+    ap.add_argument("--allreduce-log", type=str, default=None)
+    ap.add_argument("--workers", type=int, default=4)
+    ap.add_argument("--layers", type=str, default=None)
     args = ap.parse_args(argv)
-    if args.models or not args.log:
+    from . import comm_logs as cl
+    if args.p2p:
+        sizes, mean, _ = cl.read_allreduce_log(args.p2p)
+        alpha, beta = cl.fit_alpha_beta(sizes, mean)
+        print("point-to-point fit over %d sizes: alpha = %.6f, beta = %.9f per unit of size" % (len(sizes), alpha, beta))
+    if args.allreduce_log:
+        sizes, mean, _ = cl.read_allreduce_log(args.allreduce_log)
+        pred = cl.predict_allreduce(sizes, args.workers)
+        print("all-reduce on %d workers, %d sizes: mean relative error of the ring model %.3f"
+              % (args.workers, len(sizes), cl.relative_error(mean, pred)))
+    if args.layers:
+        sizes, comms, computes, _ = cl.read_layer_log(args.layers)
+        print("layers:", dict(cl.gradient_size_statistics(sizes)))
+        sim = cm.Simulator(args.layers, computes, sizes, args.workers)
+        print("iteration time [ms]: WFBP %.3f, single all-reduce %.3f, merged %.3f"
+              % (sim.wfbp(comms).total_ms, sim.single_allreduce().total_ms, sim.mg_wfbp().total_ms))
+    if args.models or not (args.log or args.p2p or args.allreduce_log or args.layers):
         print("all-reduce models, m=%d elements, rho=%g (ms, 1 GbE constants)" % (args.m, args.rho))
         print("%6s %12s %12s %12s" % ("P", "dense", "topk", "gtopk"))
         for p in (4, 8, 16, 32, 64, 128):

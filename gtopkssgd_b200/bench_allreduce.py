@@ -8,7 +8,7 @@ residual.  Timed per call on the device (CUDA events, max over ranks):
   ours_ms    K1 fused select + K2 persistent exchange (+ residual put-back)
   k1_ms/k2_ms the two parts separately
   dense_ms   NCCL all-reduce of the same d floats (the dense baseline)
-  rehost_ms  the reference's algorithm re-hosted on this box: torch.topk on the
+  rehost_ms  the reference's algorithm re-hosted on today's PyTorch: torch.topk on the
              device, D2H of the k pairs, recursive-doubling tree over gloo
              send/recv with numpy merges on the host, H2D, scatter
              (the op sequence of allreducer.py:429-478 + 71-163; the unmodified
@@ -28,7 +28,7 @@ import time
 import torch
 import torch.distributed as dist
 
-NVLINK_GBS = 770.0  # measured peer copy bandwidth per direction on this pool
+NVLINK_GBS = 770.0  # measured peer copy bandwidth per direction (NVLink 5 through NVSwitch, nominal 900)
 PREQUEUE_CYCLES = 0  # set by --prequeue
 
 

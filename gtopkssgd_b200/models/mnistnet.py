@@ -17,4 +17,4 @@ class MnistNet(nn.Module):
         x = F.relu(F.max_pool2d(self.conv1(x), 2))
         x = F.relu(F.max_pool2d(self.conv2_drop(self.conv2(x)), 2))
         x = F.dropout(F.relu(self.fc1(x.view(-1, 320))), training=self.training)
-        return F.log_softmax(self.fc2(x), dim=1)
+        return self.fc2(x)  # logits, as the reference returns them (dl_trainer.py:68-75)

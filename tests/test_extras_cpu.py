@@ -177,3 +177,74 @@ def test_clock_sampler_parses_and_falls_back(monkeypatch):
     out = c.stop()
     assert out["sm_mhz"] == 1950.0 and out["sm_max_mhz"] == 1965.0 and out["samples"] == 1
     assert out["reasons"] == ["sw_power_cap"] and out["power_w_max"] == 640.5
+
+
+# ---- offline analysis: communication logs, fits, timelines ------------------------------------------------
+def test_comm_log_readers_and_alpha_beta_fit(tmp_path):
+    """Synthetic logs in the formats the paper scripts read (scripts/icdcs2019/communication.py:235-309,
+    557-586, utils.py:4-53, plot_sth.py:117-136)."""
+    import numpy as np
+    from gtopkssgd_b200.analysis import comm_logs as cl
+    from gtopkssgd_b200.analysis import cost_models as cm
+    # nccl-tests table: 12 columns, size first, out-of-place time fifth
+    nccl = tmp_path / "nccl.log"
+    rows = ["# nThread 1 nGpus 8", "#       size         count      type   redop     time   algbw   busbw  error     time   algbw   busbw  error",
+            "           8             2     float     sum    10.00    0.00    0.00  0e+00    10.0    0.00    0.00  0e+00"]
+    for size in (1024, 16384, 65536, 1 << 20, 1 << 23):
+        rows.append("%12d %12d     float     sum   %7.2f    1.00    1.75  0e+00   %7.2f    1.00    1.75  0e+00"
+                    % (size, size // 4, 20 + size / 1e5, 21 + size / 1e5))
+    nccl.write_text("\n".join(rows) + "\n")
+    sizes, times = cl.read_nccl_tests_log(str(nccl))
+    assert sizes == [16384, 65536, 1 << 20]           # 8 bytes, below and above the window dropped
+    assert times[0] == pytest.approx(20 + 16384 / 1e5, abs=0.01)
+    # MPI probe: "<size> <...> <time>", several samples per size, comments skipped
+    alpha, beta = 0.436, 3.6e-5
+    probe = tmp_path / "p2platency.log"
+    rng = np.random.RandomState(0)
+    lines = ["# size iters time", "[rank 0] warm-up"]
+    for size in (16384, 65536, 262144, 1 << 20, 1 << 22):
+        for _ in range(5):
+            lines.append("%d 10 %.6f" % (size, (alpha + beta * size) * 1000.0 + rng.normal(0, 1e-3)))
+    probe.write_text("\n".join(lines) + "\n")
+    s, mean, std = cl.read_allreduce_log(str(probe))
+    assert s == [16384, 65536, 262144, 1 << 20, 1 << 22] and all(x < 0.01 for x in std)
+    a, b = cl.fit_alpha_beta(s, [m / 1000.0 for m in mean])
+    assert a == pytest.approx(alpha, rel=1e-2) and b == pytest.approx(beta, rel=1e-3)
+    pred = cl.predict_allreduce(s, 8)
+    assert pred == [cm.ring_allreduce_us(8, float(m)) for m in s] and pred[0] < pred[-1]
+    assert cl.relative_error(pred, pred) == 0.0
+    # "<nodes>,<size> ... <time>"
+    nodes = tmp_path / "nodes.log"
+    nodes.write_text("# header line here\n4,1024 x 0.5000\n4,2048 x 0.7500\n")
+    assert cl.read_node_allreduce_log(str(nodes)) == (4, [1024, 2048], [0.5, 0.75])
+    # per-layer records and the compute-only CSV
+    layers = tmp_path / "layers.log"
+    layers.write_text("I0 comm [0, 1000.0, 120.0, 80.0, 90.0]\n"
+                      "I0 comm [1, 2000.0, 0.4, 80.0, 90.0]\n"       # compute truncates to 0: skipped
+                      "I0 comm [2, 4000000.0, 300.0, 500.0, 510.0]\n")
+    sz, comms, comps, merged = cl.read_layer_log(str(layers))
+    assert sz == [1000.0, 4000000.0] and comps == [120.0, 300.0] and comms == merged == [90.0, 510.0]
+    st = cl.gradient_size_statistics(sz)
+    assert st["layers"] == 2 and st["total"] == 4001000.0 and st["below_1m_fraction"] == 0.5
+    csv = tmp_path / "p100.log"
+    csv.write_text("conv1,w,100,5.0\nconv1,b,10,5.0\nfc,w,4000,9.0\n")
+    raw, layer_comp, layer_size = cl.read_compute_log(str(csv))
+    assert raw == [100.0, 10.0, 4000.0] and layer_comp == [5.0, 9.0] and layer_size == [110.0, 4000.0]
+    # the layer log drives the timeline simulator
+    sim = cm.Simulator("t", comps, sz, 4)
+    assert sim.mg_wfbp().total_ms <= sim.wfbp().total_ms + 1e-9
+
+
+def test_figures_render_or_say_that_matplotlib_is_missing(tmp_path):
+    from gtopkssgd_b200.analysis import cost_models as cm
+    from gtopkssgd_b200.analysis import plots
+    sim = cm.Simulator("t", [100.0, 200.0, 50.0], [1e5, 4e6, 2e4], 4)
+    tls = {"wfbp": sim.wfbp(), "single": sim.single_allreduce(), "merged": sim.mg_wfbp()}
+    try:
+        import matplotlib  # noqa: F401
+    except ImportError:
+        with pytest.raises(ImportError, match="matplotlib"):
+            plots.plot_timeline(tls, str(tmp_path / "t.png"))
+        return
+    out = plots.plot_timeline(tls, str(tmp_path / "t.png"))
+    assert os.path.getsize(out) > 0
