@@ -7,6 +7,10 @@ For every (d, rho): fp32 vectors N(0, 1e-2) with a fresh seed per rank, zero
 residual.  Timed per call on the device (CUDA events, max over ranks):
   ours_ms    K1 fused select + K2 persistent exchange (+ residual put-back)
   k1_ms/k2_ms the two parts separately
+  *_chain_ms  the same per call, measured over 20 calls back to back (steady
+             state: no host barrier, hence no start skew, between the calls)
+  k2_trace_us device-side phase stamps of one exchange on every rank
+             (``ops.exchange.decode_k2_trace``): time in flag waits and in work
   dense_ms   NCCL all-reduce of the same d floats (the dense baseline)
   rehost_ms  the reference's algorithm re-hosted on today's PyTorch: torch.topk on the
              device, D2H of the k pairs, recursive-doubling tree over gloo
@@ -54,6 +58,26 @@ def _timed(fn, iters, warmup, device, setup=None):
         torch.cuda.synchronize()
         total += a.elapsed_time(b)
     return comm.allreduce_max_float(total / iters, device)
+
+
+def _timed_chain(fn, device, n=20, warmup=3, setup=None):
+    """Steady-state time per call: n calls back to back on one stream between two events.  After the
+    first call the ranks pace one another through the exchange itself, so the start skew that a host
+    barrier leaves (tens of microseconds) is paid once, not once per call as in ``_timed``."""
+    from .parallel import comm
+    for _ in range(warmup):
+        fn()
+    if setup:
+        setup()
+    comm.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return comm.allreduce_max_float(a.elapsed_time(b) / n, device)
 
 
 def _rehost_reference(g, resid, k, world, rank):
@@ -107,18 +131,30 @@ def run_config(d, rho, iters=10, warmup=3, with_dense=True, with_rehost=True):
     row["k1_ms"] = _timed(k1, iters, warmup, dev, setup=resid.zero_)
     if world > 1:
         row["k2_ms"] = _timed(k2, iters, warmup, dev)
+        row["k2_chain_ms"] = _timed_chain(k2, dev)
+        row["ours_chain_ms"] = _timed_chain(both, dev, setup=resid.zero_)
+        # device-side phase stamps of one more call, from every rank
+        k1()
+        k2()
+        torch.cuda.synchronize()
+        traces = [None] * world
+        dist.all_gather_object(traces, rc.trace(), group=comm.cpu_group())
+        row["k2_trace_us"] = traces
+        row["k2_in_kernel_us"] = max((t.get("total", 0.0) for t in traces), default=0.0)
+        row["k2_work_us"] = max((t.get("work", 0.0) for t in traces), default=0.0)
         status = rc.status()
         row["status"] = list(status)
         rounds = int(math.log2(world))
         wire = 2.0 * k * rounds * 8
         row["nvlink_roofline_ms"] = wire / (NVLINK_GBS * 1e9) * 1e3
-        row["k2_frac_of_nvlink_roofline"] = row["nvlink_roofline_ms"] / row["k2_ms"]
+        row["k2_frac_of_nvlink_roofline"] = row["nvlink_roofline_ms"] / row["k2_chain_ms"]
     row["k1_hbm_roofline_ms"] = 12.0 * d / (6550.1e9) * 1e3
     st = sel.stats()
     row["k1_fallbacks"] = st["n_fallbacks"]
     if with_dense and world > 1:
         buf = grads[0].clone()
         row["dense_nccl_ms"] = _timed(lambda: dist.all_reduce(buf), iters, warmup, dev)
+        row["dense_nccl_chain_ms"] = _timed_chain(lambda: dist.all_reduce(buf), dev)
     if with_rehost and world > 1 and (world & (world - 1)) == 0:
         r2 = torch.zeros(d, device=dev)
         row["rehost_ref_ms"] = _timed(lambda: _rehost_reference(grads[0], r2, k, world, rank), max(3, iters // 2), 1,

@@ -44,14 +44,48 @@ def get_audio_length(path: str) -> float:
         return w.getnframes() / float(w.getframerate())
 
 
-def load_randomly_augmented_audio(path, sample_rate=16000, tempo_range=(0.85, 1.15), gain_range=(-6, 8)):
-    """Random speed and gain perturbation of one utterance."""
+def _wav_rate(path: str) -> int:
+    with wave.open(path, "rb") as w:
+        return int(w.getframerate())
+
+
+def load_audio_segment(path: str, sample_rate: int, start_time: float, end_time: float) -> np.ndarray:
+    """The samples between ``start_time`` and ``end_time`` (seconds) of a recording, mono, resampled to
+    ``sample_rate``.  In-process counterpart of the reference's ``audio_with_sox``
+    (audio_data/data_loader.py:277-289: ``sox ... trim start =end`` into a temporary file)."""
     from scipy.signal import resample
     y = load_audio(path)
+    rate = _wav_rate(path)
+    lo = max(int(round(start_time * rate)), 0)
+    hi = min(int(round(end_time * rate)), len(y))
+    seg = y[lo:max(hi, lo)]
+    if rate != sample_rate and len(seg):
+        seg = resample(seg, max(int(round(len(seg) * sample_rate / float(rate))), 1)).astype(np.float32)
+    return seg.astype(np.float32)
+
+
+audio_with_sox = load_audio_segment  # the reference's name for it
+
+
+def augment_audio(path: str, sample_rate: int, tempo: float, gain: float) -> np.ndarray:
+    """Tempo (speed factor) and gain (dB) applied to one recording, resampled to ``sample_rate``
+    (reference: ``augment_audio_with_sox``, audio_data/data_loader.py:292-305)."""
+    from scipy.signal import resample
+    y = load_audio(path)
+    rate = _wav_rate(path)
+    n = max(int(round(len(y) / tempo * sample_rate / float(rate))), 1)
+    y = resample(y, n).astype(np.float32)
+    return np.clip(y * (10.0 ** (gain / 20.0)), -1.0, 1.0)
+
+
+augment_audio_with_sox = augment_audio
+
+
+def load_randomly_augmented_audio(path, sample_rate=16000, tempo_range=(0.85, 1.15), gain_range=(-6, 8)):
+    """Random speed and gain perturbation of one utterance."""
     tempo = np.random.uniform(*tempo_range)
     gain_db = np.random.uniform(*gain_range)
-    y = resample(y, max(int(round(len(y) / tempo)), 1)).astype(np.float32)
-    return np.clip(y * (10.0 ** (gain_db / 20.0)), -1.0, 1.0)
+    return augment_audio(path, sample_rate, tempo, gain_db)
 
 
 class NoiseInjection:

@@ -248,3 +248,27 @@ def test_figures_render_or_say_that_matplotlib_is_missing(tmp_path):
         return
     out = plots.plot_timeline(tls, str(tmp_path / "t.png"))
     assert os.path.getsize(out) > 0
+
+
+def test_audio_segment_and_augment(tmp_path):
+    """Cropping a recording by time with resampling (the reference's audio_with_sox,
+    audio_data/data_loader.py:277-289) and the tempo/gain perturbation, in process."""
+    from gtopkssgd_b200.data import audio
+    rate = 8000
+    t = np.arange(rate * 2) / rate
+    pcm = (np.sin(2 * np.pi * 440 * t) * 0.5 * 32767).astype(np.int16)
+    path = str(tmp_path / "tone.wav")
+    with wave.open(path, "wb") as w:
+        w.setnchannels(1)
+        w.setsampwidth(2)
+        w.setframerate(rate)
+        w.writeframes(pcm.tobytes())
+    seg = audio.load_audio_segment(path, 16000, 0.5, 1.0)
+    assert seg.dtype == np.float32 and abs(len(seg) - 8000) <= 1            # 0.5 s at 16 kHz
+    assert 0.3 < float(np.abs(seg).max()) < 0.6
+    same = audio.audio_with_sox(path, rate, 0.25, 0.75)
+    assert len(same) == 4000 and np.allclose(same, audio.load_audio(path)[2000:6000])
+    assert len(audio.load_audio_segment(path, rate, 1.9, 5.0)) == 800       # clipped to the end of the file
+    fast = audio.augment_audio(path, rate, tempo=2.0, gain=-6.0)
+    assert abs(len(fast) - rate) <= 1 and float(np.abs(fast).max()) == pytest.approx(0.25, rel=0.1)
+    assert audio.augment_audio_with_sox is audio.augment_audio
