@@ -20,6 +20,10 @@ from ..utils.misc import force_insert_item, topk  # noqa: F401
 from . import fallback
 
 THRESHOLD = settings.THRESHOLD
+# value types that may travel (the reference's MPI_TYPES, allreducer.py:19-24: fp32, and a
+# two-byte type registered for fp16)
+WIRE_TYPES = {np.float32: torch.float32, np.float16: torch.float16, np.dtype("float32"): torch.float32,
+              np.dtype("float16"): torch.float16}
 
 
 def _as_numpy(x):
@@ -58,7 +62,8 @@ def topk_sparse_allreduce(comm, sparse_tensor, storage, indexes=None, dtype=np.f
         indexes = _as_numpy(indexes)
         values = tensor
     ai, av = fallback.topk_allgather(torch.from_numpy(indexes.astype(np.int64)),
-                                     torch.from_numpy(values.astype(np.float32)), group=comm)
+                                     torch.from_numpy(values.astype(np.float32)), group=comm,
+                                     wire_dtype=WIRE_TYPES.get(dtype, torch.float32))
     return av.numpy().astype(dtype), ai.numpy().astype(np.uint32), None
 
 

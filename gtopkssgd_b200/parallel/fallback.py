@@ -83,17 +83,23 @@ def gtopk_allreduce(idx: torch.Tensor, val: torch.Tensor, k: int, group=None,
     return gi, gv
 
 
-def topk_allgather(idx: torch.Tensor, val: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """All P selections concatenated in rank order: (P*k indices, P*k values)."""
+def topk_allgather(idx: torch.Tensor, val: torch.Tensor, group=None,
+                   wire_dtype: torch.dtype = torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All P selections concatenated in rank order: (P*k indices, P*k values).
+    ``wire_dtype=torch.float16`` sends the values in half precision (two bytes per
+    value on the wire; the reference registers such an MPI type, allreducer.py:19-24,
+    and casts the gathered values to it, :52-53); every rank, the sender included,
+    then sees the same rounded values, returned as fp32."""
+    idx = idx.cpu().to(torch.int64).contiguous()
+    val = val.cpu().to(torch.float32).to(wire_dtype).contiguous()
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
-        return idx, val
+        return idx, val.to(torch.float32)
     world = dist.get_world_size(group)
-    idx, val = idx.cpu().to(torch.int64).contiguous(), val.cpu().to(torch.float32).contiguous()
     all_i = [torch.empty_like(idx) for _ in range(world)]
     all_v = [torch.empty_like(val) for _ in range(world)]
     dist.all_gather(all_i, idx, group=group)
     dist.all_gather(all_v, val, group=group)
-    return torch.cat(all_i), torch.cat(all_v)
+    return torch.cat(all_i), torch.cat(all_v).to(torch.float32)
 
 
 def dense_allreduce(tensor: torch.Tensor, group=None) -> torch.Tensor:

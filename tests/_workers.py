@@ -413,3 +413,16 @@ def selfcheck_worker(rank, world, compressor):
     dopt.stop()
     comm.shutdown()
     return out
+
+
+def fp16_wire_worker(rank, world):
+    """Top-k all-gather with half-precision values on the wire (reference: allreducer.py:19-24, 52-53)."""
+    import numpy as np
+    from gtopkssgd_b200.parallel import comm, compat
+    torch.set_num_threads(1)
+    comm.init(backend="gloo", timeout_s=30)
+    idx = np.arange(4, dtype=np.int64) + 10 * rank
+    val = (np.arange(4, dtype=np.float32) + 1.0) * (1.0 + rank) / 3.0
+    v, i, _ = compat.topk_sparse_allreduce(comm.cpu_group(), val, {}, indexes=idx, dtype=np.float16)
+    comm.shutdown()
+    return {"v": v, "i": i}

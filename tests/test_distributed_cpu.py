@@ -170,3 +170,12 @@ def test_exchange_selfcheck_on_gloo_ranks(world, compressor):
         assert o["ok"], o
         assert len(o["groups"]) >= 2 and o["max_rel_err"] <= 1e-5
         assert all(g["index_sets_equal"] and g["residual_ok_all_ranks"] and g["select_ok_all_ranks"] for g in o["groups"])
+
+
+def test_topk_allgather_with_half_precision_wire_values():
+    import numpy as np
+    out = spawn_ranks(_workers.fp16_wire_worker, 2, timeout_s=120)
+    want_v = np.concatenate([((np.arange(4, dtype=np.float32) + 1.0) * (1.0 + r) / 3.0).astype(np.float16) for r in range(2)])
+    want_i = np.concatenate([np.arange(4) + 10 * r for r in range(2)]).astype(np.uint32)
+    for o in out:
+        assert o["v"].dtype == np.float16 and np.array_equal(o["v"], want_v) and np.array_equal(o["i"], want_i)

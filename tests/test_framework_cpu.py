@@ -233,6 +233,10 @@ def test_compat_functions_single_process():
     v1, i1, none = compat.topk_sparse_allreduce(None, vals, {}, indexes=idx)
     assert none is None and len(v1) == 10
     assert np.allclose(compat.dense_allreduce(None, dense), dense)
+    # half-precision wire type of the all-gather variant (allreducer.py:19-24, 52-53)
+    v16, i16, _ = compat.topk_sparse_allreduce(None, vals, {}, indexes=idx, dtype=np.float16)
+    assert v16.dtype == np.float16 and np.array_equal(i16, i1)
+    assert np.allclose(v16.astype(np.float32), vals, rtol=1e-3, atol=1e-4)
 
 
 def test_ptb_reader_windows(tmp_path):
