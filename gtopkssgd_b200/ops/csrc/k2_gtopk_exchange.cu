@@ -36,7 +36,8 @@
 
 namespace gtk {
 
-constexpr int kK2Cache = 4;  // union entries each thread keeps in registers across the phases of a round
+// kK2Cache = union entries each thread keeps in registers across the phases of a round (template
+// parameter of the kernel: 4 by default, 8 when a 16-CTA cluster serves up to 64 K union entries).
 
 struct K2Shared {
   ExchangeShared ex;
@@ -58,6 +59,7 @@ __device__ __forceinline__ void hist0_flush(K2Shared& sh, unsigned int* ghist) {
   __syncthreads();
 }
 
+template <int kK2Cache>
 __global__ void __launch_bounds__(kSelThreads)
 k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsigned int P,
                   unsigned int k, unsigned int kcap, unsigned int d, unsigned long long limit_ns,
@@ -433,17 +435,29 @@ extern "C" int gtk_k2rank_fill(void* desc_host, const void* sel, const void* st,
   return GTK_OK;
 }
 
-static int k2_max_coresident(void* fn) {
-  static int cached = 0;  // the occupancy query costs microseconds; the answer never changes
-  if (cached) return cached;
+using K2Kernel = void (*)(const K2Rank*, unsigned int, unsigned int, unsigned int, unsigned int, unsigned int,
+                          unsigned long long, int);
+
+// Register-cache depth for a launch: 8 entries per thread when a cluster's threads would otherwise
+// have to re-read part of the union from memory in every phase, 4 otherwise.
+static int k2_cache_depth(unsigned int k, unsigned int nctas, int cluster) {
+  const unsigned long long per_thread4 = 4ull * nctas * kSelThreads;
+  return (cluster && 2ull * k > per_thread4) ? 8 : 4;
+}
+static K2Kernel k2_kernel(int depth) { return depth == 8 ? k2_gtopk_exchange<8> : k2_gtopk_exchange<4>; }
+
+static int k2_max_coresident(int depth) {
+  static int cached[2] = {0, 0};  // the occupancy query costs microseconds; the answer never changes
+  int& c = cached[depth == 8];
+  if (c) return c;
   const DeviceInfo* di = gtk_device_info();
   if (!di) return 0;
   int occ = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)fn, kSelThreads, 0) !=
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)k2_kernel(depth), kSelThreads, 0) !=
       cudaSuccess)
     return 0;
-  cached = occ * di->sms;
-  return cached;
+  c = occ * di->sms;
+  return c;
 }
 
 // Largest cluster (CTAs of one rank joined by the hardware barrier) that `nranks` ranks can hold
@@ -456,28 +470,31 @@ static bool k2_cluster_fits(unsigned int nranks, unsigned int nctas) {
   c = 2;
   const DeviceInfo* di = gtk_device_info();
   if (!di || !di->cluster) return false;
-  if (nctas > 8 && cudaFuncSetAttribute((const void*)k2_gtopk_exchange,
-                                        cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
-    cudaGetLastError();
-    return false;
+  for (int depth : {4, 8}) {
+    if (nctas > 8 && cudaFuncSetAttribute((const void*)k2_kernel(depth),
+                                          cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nctas, nranks);
+    cfg.blockDim = dim3(kSelThreads);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int nclusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&nclusters, (const void*)k2_kernel(depth), &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    if (nclusters < (int)nranks) return false;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(nctas, nranks);
-  cfg.blockDim = dim3(kSelThreads);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = nctas;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int nclusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&nclusters, (const void*)k2_gtopk_exchange, &cfg) != cudaSuccess) {
-    cudaGetLastError();
-    return false;
-  }
-  if (nclusters >= (int)nranks) c = 1;
-  return c == 1;
+  c = 1;
+  return true;
 }
 
 // ranks_dev: device array of nranks_in_launch K2Rank descriptors (1 in production).  Nothing is
@@ -491,10 +508,11 @@ extern "C" int gtk_k2_exchange(const void* ranks_dev, unsigned int nranks, unsig
   cudaStream_t stream = (cudaStream_t)stream_;
   if (P < 2 || (P & (P - 1)) != 0 || P > (unsigned int)kMaxPeers) return GTK_ERR_ARG;
   if (k == 0 || k > kcap || nranks == 0 || nctas == 0) return GTK_ERR_ARG;
-  const int maxco = k2_max_coresident((void*)k2_gtopk_exchange);
-  if ((int)(nranks * nctas) > maxco) return GTK_ERR_ARG;
   const K2Rank* ranks = (const K2Rank*)ranks_dev;
   int cluster = (use_cluster && k2_cluster_fits(nranks, nctas)) ? 1 : 0;
+  const int depth = k2_cache_depth(k, nctas, cluster);
+  const K2Kernel fn = k2_kernel(depth);
+  if ((int)(nranks * nctas) > k2_max_coresident(depth)) return GTK_ERR_ARG;
   void* args[] = {&ranks, &rank_base, &P, &k, &kcap, &d, &limit_ns, &cluster};
   cudaError_t e;
   if (cluster) {
@@ -511,14 +529,13 @@ extern "C" int gtk_k2_exchange(const void* ranks_dev, unsigned int nranks, unsig
     attr[1].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = nranks > 1 ? 2 : 1;  // one cluster is co-scheduled by the hardware anyway
-    e = cudaLaunchKernelExC(&cfg, (const void*)k2_gtopk_exchange, args);
+    e = cudaLaunchKernelExC(&cfg, (const void*)fn, args);
   } else if (nranks * nctas == 1) {
     // one CTA waits on nobody of its own launch: a plain launch
-    k2_gtopk_exchange<<<dim3(1, 1), dim3(kSelThreads), 0, stream>>>(ranks, rank_base, P, k, kcap, d, limit_ns, 0);
+    fn<<<dim3(1, 1), dim3(kSelThreads), 0, stream>>>(ranks, rank_base, P, k, kcap, d, limit_ns, 0);
     e = cudaGetLastError();
   } else {
-    e = cudaLaunchCooperativeKernel((void*)k2_gtopk_exchange, dim3(nctas, nranks), dim3(kSelThreads),
-                                    args, 0, stream);
+    e = cudaLaunchCooperativeKernel((void*)fn, dim3(nctas, nranks), dim3(kSelThreads), args, 0, stream);
   }
   gtk_count_launch(1);
   if (e != cudaSuccess) return GTK_ERR_CUDA;

