@@ -42,6 +42,8 @@ namespace gtk {
 struct K2Shared {
   ExchangeShared ex;
   unsigned int hist0[kHistBins];  // this CTA's share of the first-digit histogram, built on the fly
+  unsigned int cursor;            // single-CTA ranks: output cursor and tie tickets of the current round
+  unsigned int tie;               // live here instead of in global memory (two round trips less per round)
 };
 
 __device__ __forceinline__ void hist0_clear(K2Shared& sh) {
@@ -299,10 +301,16 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       if (last)
         for (unsigned int q = 1; q < P; ++q) st_pair(R.peer_gout[q] + (size_t)parity * kcap + pos, e);
     };
-    StagedAppender app{&ss, OUT, &ctrl->cursor[r], kcap, ctrl};
-    app.begin();
+    unsigned int* const cursor = single ? &sh.cursor : &ctrl->cursor[r];
+    unsigned int* const tie = single ? &sh.tie : &ctrl->tie[r];
+    if (single && threadIdx.x == 0) {
+      sh.cursor = 0u;
+      sh.tie = 0u;
+    }
+    StagedAppender app{&ss, OUT, cursor, kcap, ctrl};
+    app.begin();  // (a __syncthreads: the two words above are visible)
     auto consider = [&](const Pair& e) {
-      if (e.idx >= 0 && passes_threshold(mag_key(e.val), th, &ctrl->tie[r])) {
+      if (e.idx >= 0 && passes_threshold(mag_key(e.val), th, tie)) {
         app.put(e);
         if (keep) atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
       }
@@ -322,7 +330,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     if (!single && keep) hist0_flush(sh, ctrl->hist[r + 1][0]);
     if (!bar.sync(290 + r)) { fail(); return; }  // OUT and its cursor complete
     trace_stamp(ctrl, 1 + 8 * r + 5);
-    n_cur = __ldcg(&ctrl->cursor[r]);
+    n_cur = single ? sh.cursor : __ldcg(&ctrl->cursor[r]);
     if (n_cur > kcap) n_cur = kcap;
     if (send_next) {
       if (cta == 0 && threadIdx.x == 0)
