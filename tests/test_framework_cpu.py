@@ -3,6 +3,7 @@ API, LR schedules, checkpoints + evaluate, log formats, models, data."""
 import math
 import os
 import re
+import time
 
 import numpy as np
 import pytest
@@ -549,3 +550,60 @@ def test_watchdog_note_is_raised_on_the_training_thread(monkeypatch):
     assert calls == [(1, 0)]
     d.zero_grad()  # the note is consumed
     d.stop()
+
+
+def test_decode_k2_trace_roles_and_wait_accounting():
+    """The device-side stamps of the exchange kernel decoded into wait and work (pure host code)."""
+    from gtopkssgd_b200.ops.exchange import decode_k2_trace
+    # rank 0 of 4: receiver in rounds 0 and 1, then writes the global set everywhere
+    tr = {0: 0, 1: 1000, 2: 4000, 3: 4500, 4: 6000, 5: 9000, 6: 12000,        # round 0: wait 3 us
+          9: 12500, 10: 20500, 11: 20500, 12: 22000, 13: 25000, 14: 28000,      # round 1: wait 8 us
+          40: 28100, 41: 28100, 42: 30000}
+    d = decode_k2_trace(tr, 0, 4)
+    assert d["complete"] and d["total"] == 30.0 and d["wait"] == pytest.approx(11.0) and d["work"] == pytest.approx(19.0)
+    assert [r["role"] for r in d["rounds"]] == ["recv", "recv"] and d["rounds"][1]["select"] == pytest.approx(3.0)
+    # rank 1: round-0 sender, then waits for the broadcast
+    tr1 = {0: 0, 7: 2000, 8: 3500, 40: 25000, 41: 27000, 42: 29000}
+    d1 = decode_k2_trace(tr1, 1, 4)
+    assert d1["rounds"][0] == {"role": "send", "push": 2.0, "flag": 1.5} and d1["bcast_wait"] == pytest.approx(21.5)
+    assert d1["wait"] == pytest.approx(21.5) and d1["put_back"] == 2.0
+    # rank 2: receiver in round 0, compacts straight into rank 0's slot (flag stamp of round 1), then waits
+    tr2 = {0: 0, 1: 500, 2: 2500, 3: 3000, 4: 4000, 5: 6000, 6: 8000, 16: 8500, 40: 20000, 41: 21000, 42: 22000}
+    d2 = decode_k2_trace(tr2, 2, 4)
+    assert d2["rounds"][0]["role"] == "recv" and d2["rounds"][1].get("sent") is None and d2["rounds"][1]["role"] == "send"
+    assert d2["wait"] == pytest.approx(2.0 + 11.5)
+    assert decode_k2_trace({0: 0, 1: 5}, 0, 2) == {"complete": False}
+
+
+def test_queue_driven_allreducer_signals_done_once_per_iteration(monkeypatch):
+    """The reference's thread protocol (allreducer.py:497-597): parameter names arrive through a queue in
+    backward order, a merged group is reduced when its last name is there, and "DONE" is posted once,
+    after ALL groups of the iteration, not after the first one."""
+    import queue
+    import threading
+    from gtopkssgd_b200.parallel.allreducer import AllReducer
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+    torch.manual_seed(0)
+    net, _ = create_net(10, "mnistnet")
+    q1, q2 = queue.Queue(), queue.Queue()
+    ar = AllReducer(net.named_parameters(), compression=compressors["gtopk"], sparse=True, density=0.01,
+                    msg_queue=q1, msg_queue2=q2, threshold=8000)
+    assert len(ar.engines) >= 2
+    reduced = []
+    orig = ar.reduce_group
+    monkeypatch.setattr(ar, "reduce_group", lambda gi: (reduced.append(gi), orig(gi))[1])
+    t = threading.Thread(target=ar.run, daemon=True)
+    t.start()
+    names = [n for n, _ in net.named_parameters()][::-1]
+    for it in range(2):
+        ar.flat.grad.normal_()
+        for i, n in enumerate(names):
+            q1.put(n)
+            if i < len(names) - 1:
+                time.sleep(0.002)
+                assert q2.empty(), "DONE before every group was reduced"
+        assert q2.get(timeout=10) == "DONE"
+        assert q2.empty() and len(reduced) == (it + 1) * len(ar.engines)
+    q1.put("STOP")
+    t.join(timeout=5)
+    assert not t.is_alive()
