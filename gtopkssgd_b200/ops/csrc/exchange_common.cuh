@@ -72,15 +72,26 @@ __device__ __forceinline__ size_t flag_off(unsigned int parity, unsigned int whi
   return (size_t)parity * kFlagsPerParity + which;
 }
 
-// All CTAs of the rank copy n pairs to dst (peer or local memory).  No fence
-// here: the caller passes the rank barrier and then one thread publishes the
-// data with a single system-scope release (release_flag), which is cumulative
-// over everything the barrier ordered before it.
+// All CTAs of the rank copy n pairs to dst (peer or local memory).  The caller
+// then calls cta_fence_peer_stores(), passes the rank barrier, and one thread
+// publishes the data with release_flag().
 __device__ __forceinline__ void push_pairs(Pair* dst, const Pair* src, unsigned int n,
                                            unsigned int cta, unsigned int nct) {
   const unsigned int stride = nct * kSelThreads;
   for (unsigned int i = cta * kSelThreads + threadIdx.x; i < n; i += stride)
     st_pair(&dst[i], ld_pair_cg(&src[i]));
+}
+
+// Called by all threads of a CTA after its last store into peer memory of a phase and before the rank's
+// barrier: one thread issues a system-scope fence on behalf of the CTA (the __syncthreads orders the
+// other threads' stores before it).  This is the pattern library collectives use per channel: the fence
+// is issued on the SM that issued the stores, so it waits for their acknowledgement from the remote
+// side.  Relying on the flag's own release alone would ask one SM's release to cover NVLink stores still
+// in flight from other SMs that it only knows through a cluster- or GPU-scope barrier; with 16-CTA
+// clusters on four GPUs a receiver was seen to read a slot before all of it had landed.
+__device__ __forceinline__ void cta_fence_peer_stores() {
+  __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
 }
 
 // Publish: st.release.sys orders every store that happens-before it (this

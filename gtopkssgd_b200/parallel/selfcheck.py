@@ -87,6 +87,15 @@ def exchange_selfcheck(optimizer, rtol: float = 1e-5) -> dict:
             row["n_global"] = len(got)
             same_everywhere = all(set(e["segs"][0][0].tolist()) == set(got) for e in everyone)
         row["index_sets_equal"] = set(got) == set(ref)
+        if not row["index_sets_equal"]:
+            # what kind of difference: entries that no rank selected in this call can only come from a
+            # receive slot that was read before (all of) this call's data had landed in it
+            union = set()
+            for li_, _ in local_sets:
+                union.update(li_.tolist())
+            extra, missing = set(got) - set(ref), set(ref) - set(got)
+            row["n_extra"], row["n_missing"] = len(extra), len(missing)
+            row["n_extra_not_in_any_local_selection"] = len(extra - union)
         row["max_rel_err"] = _max_rel_err(got, ref) if row["index_sets_equal"] else float("inf")
         row["all_ranks_same_set"] = bool(same_everywhere)
         # this rank's own select and residual

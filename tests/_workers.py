@@ -426,3 +426,45 @@ def fp16_wire_worker(rank, world):
     v, i, _ = compat.topk_sparse_allreduce(comm.cpu_group(), val, {}, indexes=idx, dtype=np.float16)
     comm.shutdown()
     return {"v": v, "i": i}
+
+
+def real_peer_exchange_worker(rank, world, d, k, nctas, epochs, mode="gtopk"):
+    """K1 + the exchange kernel between real GPUs (one process per GPU, CUDA-IPC symmetric regions),
+    without a model around it: returns, per epoch, this rank's gradient seed, its local selection,
+    the global result it holds and its residual, for the oracle comparison in the parent."""
+    from gtopkssgd_b200 import settings
+    from gtopkssgd_b200.ops import exchange as ex
+    from gtopkssgd_b200.ops.select import TopkSelector, pairs_to_tensors
+    from gtopkssgd_b200.parallel import comm
+    settings.logger.setLevel("ERROR")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    comm.init(backend="nccl", timeout_s=120)
+    with_ag = mode != "gtopk"
+    region = ex.SymmetricRegion.create_ipc(ex.region_bytes(k, with_ag), group=comm.cpu_group())
+    sel = TopkSelector(d, k, dev)
+    resid = torch.zeros(d, device=dev)
+    rc = ex.ExchangeRank(rank, world, d, k, sel, resid, region, with_allgather=with_ag, reselect=(mode == "topk2"))
+    out = {"epochs": []}
+    for e in range(epochs):
+        g = torch.Generator(device=dev).manual_seed(1000 * e + rank)
+        grad = torch.randn(d, device=dev, generator=g)
+        sel.select(grad, resid, k)
+        if mode == "gtopk":
+            ex.launch_gtopk([rc], rc.desc, rank, world, k, nctas=nctas, limit_ms=10000)
+        else:
+            ex.launch_allgather([rc], rc.desc, rc.seg_counts, rank, world, k, reselect=(mode == "topk2"), nctas=nctas,
+                                limit_ms=10000)
+        torch.cuda.synchronize()
+        li, lv = sel.pairs()
+        n = int(rc.n_global.item())
+        gout = ex.pairs_view(rc.gout_ptr(rc.last_parity()), n, dev)
+        gi, gv = pairs_to_tensors(gout, n)
+        out["epochs"].append({"local": (li.cpu(), lv.cpu()), "global": (gi.cpu(), gv.cpu()), "status": rc.status(),
+                              "resid_sum": float(resid.double().sum()), "resid": resid.cpu().clone() if d <= 2_000_000 else None,
+                              "guards": region.guards_intact()})
+    comm.barrier()
+    torch.cuda.synchronize()
+    region.close()
+    comm.shutdown()
+    return out

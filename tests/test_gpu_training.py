@@ -7,6 +7,7 @@ import torch
 
 import _workers
 from test_distributed_cpu import replay_and_check
+from gtopkssgd_b200.ops import oracle
 from gtopkssgd_b200.utils.launch import spawn_ranks
 
 pytestmark = pytest.mark.gpu
@@ -69,6 +70,49 @@ def test_eight_gpu_gtopk_matches_oracle():
     traces = spawn_ranks(_workers.resnet20_gtopk_worker, 8, args=(3, 0.001, "gtopk", "cuda"), timeout_s=300,
                          env={"NCCL_NVLS_ENABLE": "0"})
     replay_and_check(traces, 0.001, "gtopk", rtol=1e-4, atol=1e-5)
+
+
+def _check_real_peer_exchange(out, world, d, k, epochs):
+    res_ref = [torch.zeros(d) for _ in range(world)]
+    for e in range(epochs):
+        # the same Philox stream as in the workers (seed-determined, whatever the device index)
+        grads = [torch.randn(d, device="cuda:0", generator=torch.Generator(device="cuda:0").manual_seed(1000 * e + r)).cpu()
+                 for r in range(world)]
+        glob, local = oracle.simulate_gtopk_step(grads, res_ref, k)
+        ref = dict(zip(glob[0].tolist(), glob[1].tolist()))
+        for r in range(world):
+            ep = out[r]["epochs"][e]
+            assert tuple(ep["status"]) == (0, 0) and ep["guards"], (e, r, ep["status"])
+            assert set(ep["local"][0].tolist()) == set(local[r][0].tolist()), "epoch %d rank %d: local selection" % (e, r)
+            got = dict(zip(ep["global"][0].tolist(), ep["global"][1].tolist()))
+            assert len(got) == k and set(got) == set(ref), \
+                "epoch %d rank %d: %d extra, %d missing in the global set" % (e, r, len(set(got) - set(ref)), len(set(ref) - set(got)))
+            for j, v in ref.items():
+                assert got[j] == pytest.approx(v, rel=1e-5, abs=1e-6)
+            assert torch.allclose(ep["resid"], res_ref[r], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("d,k,nctas", [(1_000_000, 1000, 1), (1_000_000, 5000, 4), (2_000_000, 14000, 16),
+                                       (2_000_000, 20000, 24)])  # one CTA; clusters of 4 and 16; software barrier
+def test_exchange_kernel_between_real_gpus_matches_oracle(d, k, nctas):
+    """The multi-CTA forms of the exchange over NVLink peers: what the emulated single-GPU tests cannot
+    see is whether a partner's flag can overtake data still in flight from other SMs."""
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    epochs = 6
+    out = spawn_ranks(_workers.real_peer_exchange_worker, world, args=(d, k, nctas, epochs), timeout_s=300,
+                      env={"NCCL_NVLS_ENABLE": "0"})
+    _check_real_peer_exchange(out, world, d, k, epochs)
+
+
+@pytest.mark.multigpu
+def test_exchange_kernel_between_eight_gpus_matches_oracle():
+    if torch.cuda.device_count() < 8:
+        pytest.skip("needs 8 GPUs")
+    d, k, epochs = 2_000_000, 14000, 4
+    out = spawn_ranks(_workers.real_peer_exchange_worker, 8, args=(d, k, 16, epochs), timeout_s=300,
+                      env={"NCCL_NVLS_ENABLE": "0"})
+    _check_real_peer_exchange(out, 8, d, k, epochs)
 
 
 def test_single_gpu_cuda_graph_step_matches_oracle():
