@@ -12,6 +12,12 @@ with the batch already resident on the GPU; ``e2e`` is the same loop through
 the public trainer API (``DLTrainer.prefetch`` + ``DLTrainer.train_step``): every
 step issues one copy of a batch from pinned host memory (the next step's
 inputs, on a copy stream) and ends with the loss read back to the host.
+``comm_ms_per_iter`` is the per-iteration communication time in the benchmarked
+(graph) mode from the kernels' own device-side stamps, max over ranks: select
+(K1), exchange (K2 incl. residual put-back), split into time inside flag waits
+and work.  At N > 1 one more, checked exchange follows the timed region:
+``exchange_check`` compares the global set on the real NVLink transport, every
+rank's selection and every rank's residual with the CPU oracle's tree.
 ``--impl reference`` is the reference arm: the process is replaced by
 ``baseline/ref_arm.py``, which runs the unmodified reference on the same
 configuration and prints the same JSON shape.
@@ -250,7 +256,13 @@ def main():
                         acc["exchange_ms"] += t["total"] / 1e3
                         acc["exchange_wait_ms"] += t["wait"] / 1e3
                         acc["exchange_work_ms"] += t["work"] / 1e3
-        comm_ms = {k_: comm.allreduce_max_float(v / n_samples, device) for k_, v in acc.items()}
+        mine = {k_: v / n_samples for k_, v in acc.items()}
+        comm_ms = {k_: comm.allreduce_max_float(v, device) for k_, v in mine.items()}
+        if world > 1:  # which rank waits and which one is waited for
+            import torch.distributed as dist
+            per_rank = [None] * world
+            dist.all_gather_object(per_rank, {k_: round(v, 4) for k_, v in mine.items()}, group=comm.cpu_group())
+            comm_ms["per_rank"] = per_rank
         comm_ms.update({"ranks": "max over %d" % world, "mode": "graph" if not args.no_cuda_graph else "eager",
                         "how": "device %globaltimer stamps of K1 and K2, last step of 3 bursts of 4 further steps; exchange "
                                "= K2 from its first instruction to the end of the residual put-back, wait = time "
