@@ -607,3 +607,35 @@ def test_queue_driven_allreducer_signals_done_once_per_iteration(monkeypatch):
     q1.put("STOP")
     t.join(timeout=5)
     assert not t.is_alive()
+
+
+def test_failed_exchange_seen_on_the_host_mirror_stops_the_next_iteration(monkeypatch):
+    """The exchange kernel leaves a sticky status in its result words, which are mirrored to pinned
+    host memory behind every exchange; pre_iteration() looks at the mirror without synchronising,
+    tells err_handler and raises before anything of the next iteration is launched.  (The device
+    side of this is tests/test_gpu_kernels.py::test_k2_bounded_wait_reports_timeout; here the mirror
+    is a fake.)"""
+    from gtopkssgd_b200.parallel.allreducer import GTopkTimeout
+    monkeypatch.setattr(settings, "PIN_DENSITY", True)
+    net, _ = create_net(10, "mnistnet")
+    calls = []
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+    d = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
+                             density=0.01, err_handler=lambda n, r: calls.append((n, r)))
+
+    class FakeRankCtx:
+        def __init__(self):
+            self.words = (0, 0)
+
+        def failed_on_host_mirror(self):
+            return self.words
+
+    fake = FakeRankCtx()
+    d._allreducer.engines[0].rank_ctx = fake
+    d.zero_grad()                      # healthy mirror: nothing happens
+    fake.words = (1, 212)              # "timeout waiting for a peer flag" at code location 212
+    with pytest.raises(GTopkTimeout, match="peer flag"):
+        d.zero_grad()
+    assert calls == [(1, 0)]
+    d._allreducer.engines[0].rank_ctx = None
+    d.stop()
