@@ -106,6 +106,34 @@ def test_exchange_kernel_between_real_gpus_matches_oracle(d, k, nctas):
 
 
 @pytest.mark.multigpu
+@pytest.mark.parametrize("nctas", [1, 8])
+def test_allgather_reselect_kernel_between_real_gpus_matches_oracle(nctas):
+    """'topk2' over NVLink peers with one and with several CTAs per rank: every rank pushes its pairs into
+    every peer's all-gather slots, merges the P lists in rank order and re-selects."""
+    world = 4 if torch.cuda.device_count() >= 4 else 2
+    d, k, epochs = 1_000_000, 4000, 4
+    out = spawn_ranks(_workers.real_peer_exchange_worker, world, args=(d, k, nctas, epochs, "topk2"), timeout_s=300,
+                      env={"NCCL_NVLS_ENABLE": "0"})
+    res_ref = [torch.zeros(d) for _ in range(world)]
+    for e in range(epochs):
+        grads = [torch.randn(d, device="cuda:0", generator=torch.Generator(device="cuda:0").manual_seed(1000 * e + r)).cpu()
+                 for r in range(world)]
+        local = [oracle.compress(g, r, k) for g, r in zip(grads, res_ref)]
+        gi_ref, gv_ref = oracle.topk2_reselect(local, k)
+        for r, loc in zip(res_ref, local):
+            oracle.put_back(r, loc, gi_ref)
+        ref = dict(zip(gi_ref.tolist(), gv_ref.tolist()))
+        for r in range(world):
+            ep = out[r]["epochs"][e]
+            assert tuple(ep["status"]) == (0, 0) and ep["guards"]
+            got = dict(zip(ep["global"][0].tolist(), ep["global"][1].tolist()))
+            assert len(got) == k and set(got) == set(ref), "epoch %d rank %d" % (e, r)
+            for j, v in ref.items():
+                assert got[j] == pytest.approx(v, rel=1e-5, abs=1e-6)
+            assert torch.allclose(ep["resid"], res_ref[r], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.multigpu
 def test_exchange_kernel_between_eight_gpus_matches_oracle():
     if torch.cuda.device_count() < 8:
         pytest.skip("needs 8 GPUs")
