@@ -272,3 +272,36 @@ def test_audio_segment_and_augment(tmp_path):
     fast = audio.augment_audio(path, rate, tempo=2.0, gain=-6.0)
     assert abs(len(fast) - rate) <= 1 and float(np.abs(fast).max()) == pytest.approx(0.25, rel=0.1)
     assert audio.augment_audio_with_sox is audio.augment_audio
+
+
+def test_bench_report_tables_from_json_lines(tmp_path):
+    """The tables of measured results are built from bench.py's JSON lines (both arms) and the
+    micro-benchmark files; here from synthetic ones."""
+    import json
+    from gtopkssgd_b200.analysis import bench_report as br
+
+    def line(value, ms, e2e, impl, comm):
+        return json.dumps({"impl": impl, "value": value, "ms_per_step": ms, "e2e": {"value": e2e},
+                           "comm_ms_per_iter": comm})
+    for n in (1, 2):
+        d = tmp_path / ("n%d" % n)
+        d.mkdir()
+        (d / "ours_resnet50.json").write_text("noise before\n" + line(1000.0 * n * 0.99 ** (n - 1), 64.0, 990.0 * n, "ours",
+                                                                     {"select_ms": 0.05, "exchange_ms": 0.1, "exchange_wait_ms": 0.08}) + "\n")
+        (d / "ref_resnet50.json").write_text(line(500.0 * n * 0.9 ** (n - 1), 128.0, 495.0 * n, "reference",
+                                                  {"select_ms": 1.0, "exchange_ms": 5.0}) + "\n")
+        (d / "ref_vgg16.json").write_text(json.dumps({"impl": "reference", "unavailable": "why"}) + "\n")
+    (tmp_path / "n2" / "allreduce.json").write_text(json.dumps({"rows": [
+        {"d": 1000000, "rho": 0.001, "k": 1000, "P": 2, "ours_ms": 0.06, "k1_ms": 0.03, "k2_ms": 0.04, "k2_chain_ms": 0.025,
+         "dense_nccl_ms": 0.07, "dense_nccl_chain_ms": 0.04, "nvlink_roofline_ms": 2e-5}]}))
+    (tmp_path / "n2" / "ref_allreduce.json").write_text(json.dumps({"rows": [
+        {"d": 1000000, "rho": 0.001, "k": 1000, "P": 2, "select_ms": 0.3, "exchange_ms": 1.2, "total_ms": 1.5}]}))
+    runs = br.Runs({1: [str(tmp_path / "n1")], 2: [str(tmp_path / "missing"), str(tmp_path / "n2")]})
+    assert runs.get(1, "ref_vgg16") is None                      # an "unavailable" line is not a measurement
+    text = br.report(runs)
+    assert "| resnet50 | 2 | 1980 | 64.00 | 1980 | 900 | 128.00 | 990 | **2.00×** |" in text
+    eff = br.efficiencies(runs)
+    assert eff["ours_resnet50"][2] == pytest.approx(0.99) and eff["ref_resnet50"][2] == pytest.approx(0.9)
+    assert "**P = 2**" in text and "| 1.0 M | 0.001 | 1000 | 0.030 | 0.040 / 0.025 | 0.060 / 0.055 | 0.070 / 0.040 | 0.30 + 1.20 |" in text
+    assert "25×" in text                                          # reference total 1.5 ms / ours 0.06 ms
+    br.main(["--runs", "1=%s" % (tmp_path / "n1"), "2=%s" % (tmp_path / "n2")])
