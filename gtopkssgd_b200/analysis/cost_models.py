@@ -181,3 +181,38 @@ class Simulator:
         tl = self.wfbp(opt_c)
         tl.merged_layers = merged
         return tl
+
+
+# ---- speed-up studies built on the simulator (scripts/icdcs2019/communication.py:350-418, 420-470, 545-555) -------
+def ssgd_speedup(r: float, n: int) -> float:
+    """Speed-up of synchronous SGD on n workers when communication takes r times the compute time and
+    nothing overlaps: n / (1 + r)."""
+    return n / (1.0 + r)
+
+
+def simulated_speedups(computes: Sequence[float], sizes: Sequence[float], batch: int,
+                       nnodes: Sequence[int] = (4, 8, 16, 32, 64), comm_model=ring_allreduce_us) -> Dict[str, List[float]]:
+    """Throughput on n nodes relative to one node for three schedules of the same per-layer
+    backward times (microseconds) and gradient sizes: one all-reduce per layer as soon as its
+    gradient exists (``wfbp``), the greedily merged version (``merged``), and a single all-reduce
+    after backward (``single``).  Forward is taken as half of backward, as in the papers' script."""
+    tb = float(sum(computes)) / 1000.0          # ms
+    tf = 0.5 * tb
+    single_node = batch / (tf + tb)
+    out: Dict[str, List[float]] = {"nodes": list(nnodes), "linear": [float(n) for n in nnodes], "wfbp": [], "merged": [],
+                                   "single": []}
+    for n in nnodes:
+        sim = Simulator("sim", computes, sizes, n, comm_model=comm_model)
+        out["wfbp"].append(batch * n / (sim.wfbp().total_ms + tf) / single_node)
+        out["merged"].append(batch * n / (sim.mg_wfbp().total_ms + tf) / single_node)
+        out["single"].append(batch * n / (sim.single_allreduce().total_ms + tf) / single_node)
+    return out
+
+
+def real_comm_costs(per_gpu_pair_speeds: Sequence[float], batch: int):
+    """From measured throughputs of 1, 2, 4, ... nodes with two GPUs each (samples/s of the whole job)
+    to (compute seconds per iteration, [communication seconds at 2, 4, ... nodes]): the time per
+    iteration of a worker is batch / (per-worker throughput); what exceeds the one-node time is
+    communication (scripts/icdcs2019/communication.py:421-425)."""
+    times = [batch / ((d / 2.0) / 2 ** (i - 1)) for i, d in enumerate(per_gpu_pair_speeds)]
+    return times[0], [t - times[0] for t in times[1:]]

@@ -89,3 +89,28 @@ def parse_log(path: str, max_epochs: Optional[int] = None) -> TrainingLog:
 def mean_speed(log: TrainingLog, skip: int = 1) -> Optional[float]:
     vals = log.speeds[skip:] or log.speeds
     return sum(vals) / len(vals) if vals else None
+
+
+def read_norm_from_log(path: str):
+    """(means, stds) of the "gtopk-dense norm mean: m, std: s" lines that the error-norm diagnostic
+    logs once per epoch (scripts/icdcs2019/plot_loss.py:128-141)."""
+    means, stds = [], []
+    pat = re.compile(r"gtopk-dense norm mean: ([-\w.+]+), std: ([-\w.+]+)")
+    with open(path) as fh:
+        for line in fh:
+            m = pat.search(line)
+            if m:
+                means.append(float(m.group(1)))
+                stds.append(float(m.group(2)))
+    return means, stds
+
+
+def value_histogram(values, bins: int = 100) -> dict:
+    """Summary that the papers' ``plot_hist`` prints next to its histogram
+    (scripts/icdcs2019/utils.py:55-69): mean, std, how many values are <= 0, and the normalised
+    histogram itself."""
+    import numpy as np
+    flat = np.asarray(values, dtype=np.float64).ravel()
+    density, edges = np.histogram(flat, bins=bins, density=True) if flat.size else (np.zeros(bins), np.zeros(bins + 1))
+    return {"mean": float(flat.mean()) if flat.size else 0.0, "std": float(flat.std()) if flat.size else 0.0,
+            "non_positive": int((flat <= 0).sum()), "total": int(flat.size), "density": density, "edges": edges}

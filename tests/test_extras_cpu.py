@@ -305,3 +305,23 @@ def test_bench_report_tables_from_json_lines(tmp_path):
     assert "**P = 2**" in text and "| 1.0 M | 0.001 | 1000 | 0.030 | 0.040 / 0.025 | 0.060 / 0.055 | 0.070 / 0.040 | 0.30 + 1.20 |" in text
     assert "25×" in text                                          # reference total 1.5 ms / ours 0.06 ms
     br.main(["--runs", "1=%s" % (tmp_path / "n1"), "2=%s" % (tmp_path / "n2")])
+
+
+def test_speedup_studies_and_norm_log(tmp_path):
+    """scripts/icdcs2019/communication.py:350-418, 420-470, 545-555 and plot_loss.py:128-141 as numbers."""
+    from gtopkssgd_b200.analysis import cost_models as cm
+    from gtopkssgd_b200.analysis.log_parser import read_norm_from_log, value_histogram
+    assert cm.ssgd_speedup(0.0, 8) == 8 and cm.ssgd_speedup(1.0, 8) == 4
+    computes = [3000.0, 3500.0, 5000.0, 6000.0, 2000.0]
+    sizes = [2e6, 5e5, 4e6, 1e5, 3e6]
+    s = cm.simulated_speedups(computes, sizes, batch=32, nnodes=(4, 16))
+    assert s["nodes"] == [4, 16] and all(0 < v <= n + 1e-9 for key in ("wfbp", "merged", "single") for v, n in zip(s[key], s["nodes"]))
+    assert all(m >= w - 1e-9 for m, w in zip(s["merged"], s["wfbp"]))       # merging never loses to plain WFBP
+    comp, comms = cm.real_comm_costs([100.0, 180.0, 320.0], batch=32)
+    assert comp == pytest.approx(32 / 100.0) and comms[0] == pytest.approx(32 / 90.0 - 0.32)
+    log = tmp_path / "norm.log"
+    log.write_text("x INFO [rank:0][1] gtopk-dense norm mean: 0.125, std: 0.01\nother line\n"
+                   "x INFO [rank:0][2] gtopk-dense norm mean: 0.1, std: 0.02\n")
+    assert read_norm_from_log(str(log)) == ([0.125, 0.1], [0.01, 0.02])
+    h = value_histogram([-1.0, 0.0, 1.0, 3.0], bins=4)
+    assert h["non_positive"] == 2 and h["total"] == 4 and h["mean"] == 0.75 and len(h["density"]) == 4
