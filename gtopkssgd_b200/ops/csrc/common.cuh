@@ -46,7 +46,11 @@ struct Ctrl {
   unsigned int live[kMaxRounds + 2];
   unsigned int pad[64 - 16 - 3 * (kMaxRounds + 2)];
   unsigned long long trace[kTraceSlots];      // %globaltimer stamps of CTA 0 at phase boundaries
-  unsigned int hist[kMaxRounds + 2][3][kHistBins];  // radix histograms per round and pass
+  // Radix histograms, one set of four rows per tree round (K2) or per use (K1: sets 0-2, rows 0-2).
+  // K2 rows: 0 = first digit; 1 and 2[0..1023] = second digit of the entries whose first digit is one
+  // of three predicted ones (1024 bins each); 2[1024..] = second digit counted by a sweep when the
+  // prediction missed; 3 = third digit.
+  unsigned int hist[kMaxRounds + 2][4][kHistBins];
 };
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {

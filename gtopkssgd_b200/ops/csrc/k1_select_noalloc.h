@@ -17,7 +17,7 @@
 //     acc = g + r;  sel_out <- the k largest-magnitude (int32 idx, fp32 acc) pairs;
 //     r <- acc off the selection, 0 on it;  g is not modified.
 // The scratch memory (control block, threshold-prediction state, candidate
-// list; about 1.3 MB) lives in a file-scope static __device__ array inside the
+// list; about 1.5 MB) lives in a file-scope static __device__ array inside the
 // library, so every GPU that loads the library holds that array until the
 // process exits.  The caller passes only inputs and outputs.  No call to
 // cudaMalloc, cudaFree or any allocating library routine is made.

@@ -39,30 +39,44 @@ namespace gtk {
 // kK2Cache = union entries each thread keeps in registers across the phases of a round (template
 // parameter of the kernel: 4 by default, 8 when a 16-CTA cluster serves up to 64 K union entries).
 
+constexpr int kK2Pred = 3;  // second-digit histograms are built on the fly for this many predicted first digits
+
 struct K2Shared {
   ExchangeShared ex;
   unsigned int hist0[kHistBins];  // this CTA's share of the first-digit histogram, built on the fly
+  unsigned int hist1[kK2Pred][1024];  // second digit of the entries whose first digit is pred, pred+1, pred+2
   unsigned int cursor;            // single-CTA ranks: output cursor and tie tickets of the current round
   unsigned int tie;               // live here instead of in global memory (two round trips less per round)
 };
 
 __device__ __forceinline__ void hist0_clear(K2Shared& sh) {
   for (int i = threadIdx.x; i < kHistBins; i += kSelThreads) sh.hist0[i] = 0u;
+  for (int i = threadIdx.x; i < kK2Pred * 1024; i += kSelThreads) (&sh.hist1[0][0])[i] = 0u;
   __syncthreads();
 }
-// Adds this CTA's (possibly "negative", i.e. wrapped) partial counts to a global histogram.
-__device__ __forceinline__ void hist0_flush(K2Shared& sh, unsigned int* ghist) {
+// Global home of the second-digit histogram of predicted first digit pred + off, inside one round's set.
+__device__ __forceinline__ unsigned int* pred_row(unsigned int (*set)[kHistBins], unsigned int off) {
+  return off < 2u ? set[1] + off * 1024u : set[2];
+}
+// Adds this CTA's (possibly "negative", i.e. wrapped) partial counts to a round's global histograms
+// (first digit, and second digit for the predicted first digits) and zeroes the shared copies.
+__device__ __forceinline__ void hist0_flush(K2Shared& sh, unsigned int (*set)[kHistBins]) {
   __syncthreads();
   for (int i = threadIdx.x; i < kHistBins; i += kSelThreads) {
     const unsigned int c = sh.hist0[i];
-    if (c) atomicAdd(&ghist[i], c);
+    if (c) atomicAdd(&set[0][i], c);
     sh.hist0[i] = 0u;
+  }
+  for (int i = threadIdx.x; i < kK2Pred * 1024; i += kSelThreads) {
+    const unsigned int c = sh.hist1[i >> 10][i & 1023];
+    if (c) atomicAdd(&pred_row(set, (unsigned int)i >> 10)[i & 1023], c);
+    sh.hist1[i >> 10][i & 1023] = 0u;
   }
   __syncthreads();
 }
 
 template <int kK2Cache>
-__global__ void __launch_bounds__(kSelThreads)
+__global__ void __launch_bounds__(kSelThreads, 1)
 k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsigned int P,
                   unsigned int k, unsigned int kcap, unsigned int d, unsigned long long limit_ns,
                   int use_cluster) {
@@ -106,6 +120,18 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
   while ((1u << rounds) < P) ++rounds;
   hist0_clear(sh);
   trace_stamp(ctrl, 0);
+  // Every live entry of a round's union is counted once by its first radix digit and, if that digit is
+  // pred0, pred0 + 1 or pred0 + 2, by its second digit as well (delta = 1 adds, 0xffffffff removes).  The
+  // union's k-th magnitude is at least this rank's own, and for heavy-tailed gradients about one first
+  // digit (a factor 2^(1/8)) above it, so the re-select usually finds both digits without a sweep.
+  unsigned int pred0 = mag_key(R.st->kth_mag) >> 20;  // round 0: first digit of K1's k-th magnitude
+  auto tally = [&](float v, unsigned int delta) {
+    const uint32_t key = mag_key(v);
+    const unsigned int fd = key >> 20;
+    atomicAdd(&sh.hist0[fd], delta);
+    const unsigned int off = fd - pred0;  // wraps for fd < pred0
+    if (off < (unsigned int)kK2Pred) atomicAdd(&sh.hist1[off][(key >> 10) & 1023u], delta);
+  };
 
   for (unsigned int r = 0; r < rounds; ++r) {
     const unsigned int bit = 1u << r;
@@ -136,7 +162,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
         st_pair(&A[i], e);
         if ((unsigned int)e.idx < d) map[e.idx] = (int32_t)i;
         else record_error(ctrl, ST_BOUNDS, 300);
-        atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
+        tally(e.val, 1u);
       }
       cur_buf = 0;
     } else {
@@ -173,14 +199,14 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
         if (a.idx == e.idx) {
           const float nv = a.val + e.val;
           A[p].val = nv;  // A[p] belongs to another thread's sweep: goes through memory
-          atomicAdd(&sh.hist0[mag_key(a.val) >> 20], 0xffffffffu);
-          atomicAdd(&sh.hist0[mag_key(nv) >> 20], 1u);
+          tally(a.val, 0xffffffffu);
+          tally(nv, 1u);
           B[j].idx = -1;
           e.idx = -1;
           matched = true;
         }
       }
-      if (!matched) atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
+      if (!matched) tally(e.val, 1u);
     };
 #pragma unroll
     for (int t = 0; t < kK2Cache; ++t) {
@@ -217,8 +243,8 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
         }
       }
     }
-    if (!single) hist0_flush(sh, ctrl->hist[r][0]);
-    if (!bar.sync(240 + r)) { fail(); return; }  // sums and first-digit histogram complete
+    if (!single) hist0_flush(sh, ctrl->hist[r]);
+    if (!bar.sync(240 + r)) { fail(); return; }  // sums and the on-the-fly histograms complete
     trace_stamp(ctrl, 1 + 8 * r + 3);
 
     // ---- every thread now loads its A entries (with the merged values) next to its B entries
@@ -246,27 +272,40 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     uint32_t prefix = ss.res_digit;
     unsigned int k_rem = ss.res_krem;
     __syncthreads();
-    if (single) hist0_clear(sh);  // from here on it collects the next round's first digits
-    if (all) {
-      th.select_all = true;
-    } else {
-      // pass 1: bits 19..10 of the entries whose first digit is the threshold digit
-      smem_hist_clear(ss);
-#pragma unroll
-      for (int t = 0; t < kK2Cache; ++t)
-        if (c[t].idx >= 0 && (mag_key(c[t].val) >> 20) == prefix)
-          atomicAdd(&ss.hist[(mag_key(c[t].val) >> 10) & 1023u], 1u);
-      for (unsigned int t = kK2Cache; t < trips; ++t) {
-        const Pair e = entry(t);
-        if (e.idx >= 0 && (mag_key(e.val) >> 20) == prefix)
-          atomicAdd(&ss.hist[(mag_key(e.val) >> 10) & 1023u], 1u);
-      }
-      if (!single) smem_hist_flush(ss, ctrl->hist[r][1], 1024);
-      if (!bar.sync(250 + 10 * r)) { fail(); return; }
-      find_digit<1024>(ss, ctrl->hist[r][1], k_rem, single);
+    const unsigned int first_digit = prefix;
+    const unsigned int pred_off = first_digit - pred0;  // wraps when the threshold digit is below the prediction
+    const bool predicted = !all && pred_off < (unsigned int)kK2Pred;
+    if (predicted) {
+      // second digit: counted on the fly, no sweep and no barrier
+      find_digit_in<1024>(ss, single ? sh.hist1[pred_off] : pred_row(ctrl->hist[r], pred_off), k_rem, single);
       prefix = (prefix << 10) | ss.res_digit;
       k_rem = ss.res_krem;
       __syncthreads();
+    }
+    if (single) hist0_clear(sh);  // from here on the shared histograms collect the next round's digits
+    pred0 = all ? 0u : first_digit;  // the next union's threshold is at least this one
+    if (all) {
+      th.select_all = true;
+    } else {
+      if (!predicted) {
+        // pass 1: bits 19..10 of the entries whose first digit is the threshold digit
+        smem_hist_clear(ss);
+#pragma unroll
+        for (int t = 0; t < kK2Cache; ++t)
+          if (c[t].idx >= 0 && (mag_key(c[t].val) >> 20) == prefix)
+            atomicAdd(&ss.hist[(mag_key(c[t].val) >> 10) & 1023u], 1u);
+        for (unsigned int t = kK2Cache; t < trips; ++t) {
+          const Pair e = entry(t);
+          if (e.idx >= 0 && (mag_key(e.val) >> 20) == prefix)
+            atomicAdd(&ss.hist[(mag_key(e.val) >> 10) & 1023u], 1u);
+        }
+        if (!single) smem_hist_flush(ss, ctrl->hist[r][2] + 1024, 1024);
+        if (!bar.sync(250 + 10 * r)) { fail(); return; }
+        find_digit<1024>(ss, ctrl->hist[r][2] + 1024, k_rem, single);
+        prefix = (prefix << 10) | ss.res_digit;
+        k_rem = ss.res_krem;
+        __syncthreads();
+      }
       // pass 2: bits 9..0
       smem_hist_clear(ss);
 #pragma unroll
@@ -277,9 +316,9 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
         const Pair e = entry(t);
         if (e.idx >= 0 && (mag_key(e.val) >> 10) == prefix) atomicAdd(&ss.hist[mag_key(e.val) & 1023u], 1u);
       }
-      if (!single) smem_hist_flush(ss, ctrl->hist[r][2], 1024);
+      if (!single) smem_hist_flush(ss, ctrl->hist[r][3], 1024);
       if (!bar.sync(251 + 10 * r)) { fail(); return; }
-      find_digit<1024>(ss, ctrl->hist[r][2], k_rem, single);
+      find_digit<1024>(ss, ctrl->hist[r][3], k_rem, single);
       th.key = (prefix << 10) | ss.res_digit;
       th.quota = ss.res_krem;
       __syncthreads();
@@ -313,7 +352,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     auto consider = [&](const Pair& e) {
       if (e.idx >= 0 && passes_threshold(mag_key(e.val), th, tie)) {
         app.put(e);
-        if (keep) atomicAdd(&sh.hist0[mag_key(e.val) >> 20], 1u);
+        if (keep) tally(e.val, 1u);
       }
     };
 #pragma unroll
@@ -328,7 +367,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       app.end_tile(on_placed);
     }
     app.flush(on_placed);
-    if (!single && keep) hist0_flush(sh, ctrl->hist[r + 1][0]);
+    if (!single && keep) hist0_flush(sh, ctrl->hist[r + 1]);
     if (!keep) cta_fence_peer_stores();  // the winners went into other GPUs' memory
     if (!bar.sync(290 + r)) { fail(); return; }  // OUT and its cursor complete
     trace_stamp(ctrl, 1 + 8 * r + 5);

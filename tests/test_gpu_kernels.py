@@ -322,6 +322,37 @@ def test_k2_gtopk_exchange_emulated(P, d, k, nctas):
             assert r.region.guards_intact(), "a store landed outside the slots of rank %d" % r.rank
 
 
+@pytest.mark.parametrize("nctas", [1, 4, 12])
+def test_k2_reselect_when_the_threshold_prediction_misses(nctas):
+    """The re-select of a tree round reads its first two radix digits from histograms built on the
+    fly around a predicted threshold digit (this rank's own k-th magnitude, then the previous round's
+    threshold).  Ranks whose gradients differ in scale by orders of magnitude put the union's
+    threshold far outside that window, so the counting sweep has to take over; tiny and huge ranks
+    alternate so that both receivers and senders of every round are affected."""
+    from gtopkssgd_b200.ops import exchange as ex
+    P, d, k = 4, 300_000, 3000
+    torch.manual_seed(4242 + nctas)
+    ranks, desc = _emulated_world(P, d, k)
+    res_ref = [torch.zeros(d) for _ in range(P)]
+    scales = [1.0, 3.0e3, 1.0e-3, 5.0e1]
+    for epoch in range(3):
+        grads = [torch.randn(d, device=DEV) * scales[(r + epoch) % P] for r in range(P)]
+        for r, g in zip(ranks, grads):
+            r.selector.select(g, r.resid, k)
+        ex.launch_gtopk(ranks, desc, 0, P, k, nctas=nctas, limit_ms=2000)
+        torch.cuda.synchronize()
+        assert all(r.status() == (0, 0) for r in ranks)
+        glob, _ = oracle.simulate_gtopk_step([g.cpu() for g in grads], res_ref, k)
+        ref = dict(zip(glob[0].tolist(), glob[1].tolist()))
+        for r in ranks:
+            gi, gv = _read_gout(r, r.last_parity())
+            got = dict(zip(gi.cpu().tolist(), gv.cpu().tolist()))
+            assert set(got) == set(ref), "rank %d epoch %d" % (r.rank, epoch)
+            for j in ref:
+                assert got[j] == pytest.approx(ref[j], rel=1e-5, abs=1e-9)
+            assert torch.allclose(r.resid.cpu(), res_ref[r.rank], rtol=1e-5, atol=1e-9)
+
+
 def test_region_guard_bands_detect_a_stray_write():
     """The canary bands around a peer-visible region are checked by reading
     them back; an ordinary torch write into the band (inside the same
