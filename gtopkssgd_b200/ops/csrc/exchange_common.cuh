@@ -82,14 +82,17 @@ __device__ __forceinline__ void push_pairs(Pair* dst, const Pair* src, unsigned 
     st_pair(&dst[i], ld_pair_cg(&src[i]));
 }
 
-// Called by all threads of a CTA after its last store into peer memory of a phase and before the rank's
-// barrier: one thread issues a system-scope fence on behalf of the CTA (the __syncthreads orders the
-// other threads' stores before it).  This is the pattern library collectives use per channel: the fence
-// is issued on the SM that issued the stores, so it waits for their acknowledgement from the remote
-// side.  Relying on the flag's own release alone would ask one SM's release to cover NVLink stores still
-// in flight from other SMs that it only knows through a cluster- or GPU-scope barrier; with 16-CTA
-// clusters on four GPUs a receiver was seen to read a slot before all of it had landed.
-__device__ __forceinline__ void cta_fence_peer_stores() {
+// Called by all threads of a CTA of a multi-CTA rank after its last store into peer memory of a phase
+// and before the rank's barrier: one thread issues a system-scope fence on behalf of the CTA (the
+// __syncthreads orders the other threads' stores before it).  By the PTX memory model the flag's own
+// st.release.sys, issued after the rank's barrier, already covers these stores (the barrier is a
+// morally strong synchronisation and release is cumulative); the fence makes each SM wait for the
+// acknowledgement of its own NVLink stores instead of leaving that to one SM's release on behalf of
+// all, which is the form library collectives use (one fencing thread per CTA that stored).  A rank
+// served by a single CTA needs no extra fence: the thread that raises the flag sits in the CTA that
+// stored.  Cost: 2-3 us per sending phase.
+__device__ __forceinline__ void cta_fence_peer_stores(bool single_cta) {
+  if (single_cta) return;
   __syncthreads();
   if (threadIdx.x == 0) __threadfence_system();
 }

@@ -141,7 +141,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
       const unsigned int partner = me - bit;
       Pair* dst = R.peer_slots[partner] + slot_off(parity, r, kcap);
       push_pairs(dst, cur, n_cur, cta, nct);
-      cta_fence_peer_stores();
+      cta_fence_peer_stores(single);
       if (!bar.sync(200 + r)) { fail(); return; }
       trace_stamp(ctrl, 1 + 8 * r + 6);
       if (cta == 0 && threadIdx.x == 0)
@@ -368,7 +368,7 @@ k2_gtopk_exchange(const K2Rank* __restrict__ ranks, unsigned int rank_base, unsi
     }
     app.flush(on_placed);
     if (!single && keep) hist0_flush(sh, ctrl->hist[r + 1]);
-    if (!keep) cta_fence_peer_stores();  // the winners went into other GPUs' memory
+    if (!keep) cta_fence_peer_stores(single);  // the winners went into other GPUs' memory
     if (!bar.sync(290 + r)) { fail(); return; }  // OUT and its cursor complete
     trace_stamp(ctrl, 1 + 8 * r + 5);
     n_cur = single ? sh.cursor : __ldcg(&ctrl->cursor[r]);

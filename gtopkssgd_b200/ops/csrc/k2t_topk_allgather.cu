@@ -58,7 +58,7 @@ k2t_topk_allgather(const K2Rank* __restrict__ ranks, unsigned int rank_base, uns
     Pair* dst = (q == me ? R.ag : R.peer_ag[q]) + ag_off(parity, me, kcap);
     push_pairs(dst, R.sel, n_sel, cta, nct);
   }
-  cta_fence_peer_stores();
+  cta_fence_peer_stores(nct == 1);
   if (!bar.sync(500)) { fail(); return; }
   if (cta == 0 && threadIdx.x < P && threadIdx.x != me)  // one releasing thread per destination
     release_flag(R.peer_flags[threadIdx.x] + flag_off(parity, kFlagAg0 + me), epoch, n_sel);
