@@ -82,9 +82,11 @@ def bench_k1(d: int, rho: float, peak: float, flush: bool):
     med, best = _Timer(flush).time(fn, setup=setup)
     st = sel.stats()
     gbs = 12.0 * d / med / 1e9
+    # %globaltimer stamps of the last call (slot meanings: TopkSelector.trace)
+    stamps = {str(s): v / 1e3 for s, v in sel.trace().items()}
     return {"kernel": "k1_select", "d": d, "rho": rho, "k": k, "ms": med * 1e3, "best_ms": best * 1e3,
             "GBps": gbs, "frac_of_measured_hbm": gbs / peak, "n_cand": st["n_cand"],
-            "fallbacks": st["n_fallbacks"], "calls": st["n_calls"]}
+            "fallbacks": st["n_fallbacks"], "calls": st["n_calls"], "stamps_us": stamps}
 
 
 def bench_k3(d: int, peak: float, flush: bool):
@@ -146,8 +148,11 @@ def bench_k2_emulated(d: int, rho: float, world: int, nctas=None):
 
     med, best = _Timer(False).time(fn, iters=2 * _Timer.iters)
     bad = [r.status() for r in ranks if r.status() != (0, 0)]
+    # per-phase split of the last call from rank 0's and rank 1's %globaltimer stamps
+    phases = {"rank%d" % r.rank: r.trace() for r in ranks[:2]}
     return {"kernel": "k2_gtopk_exchange(emulated)", "d": d, "rho": rho, "k": k, "P": world,
-            "nctas": nctas or ex.default_nctas(k, world), "us": med * 1e6, "best_us": best * 1e6, "errors": bad}
+            "nctas": nctas or ex.default_nctas(k, world), "us": med * 1e6, "best_us": best * 1e6, "errors": bad,
+            "phases_us": phases}
 
 
 def bench_k2t_emulated(d: int, rho: float, world: int, reselect: bool):
