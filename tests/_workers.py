@@ -164,9 +164,12 @@ def failing_peer_worker(rank, world, mode):
     calls = []
     opt = torch.optim.SGD(net.parameters(), lr=0.1, momentum=0.9)
     dopt = DistributedOptimizer(opt, net.named_parameters(), compression=compressors["gtopk"], is_sparse=True,
-                                density=0.001, err_handler=lambda n, r: calls.append((n, r)), wait_limit_ms=1500)
+                                density=0.001, err_handler=lambda n, r: calls.append((n, r)), wait_limit_ms=3000)
     crit = torch.nn.CrossEntropyLoss()
     x, y = _make_batch(rank, 0, 4)
+    # start the good iteration together: the short wait limit is meant for the missing peer of the second
+    # iteration, not for the start-up skew between two processes on a busy host
+    torch.distributed.barrier()
     dopt.zero_grad()
     crit(net(x), y).backward()
     dopt.step()  # one good iteration with both ranks
@@ -174,7 +177,7 @@ def failing_peer_worker(rank, world, mode):
         if mode == "exit":
             os._exit(0)  # leaves between steps, nothing in flight
         if mode == "stall":
-            time.sleep(6.0)
+            time.sleep(9.0)  # three times rank 0's wait limit
             return "stalled"
     dopt.zero_grad()
     t0 = time.time()
